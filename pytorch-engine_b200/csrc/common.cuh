@@ -1,0 +1,95 @@
+// Shared device helpers: element types, reductions, the status word.
+//
+// Every kernel of this library is reached through an extern "C" launcher (see api.h) that takes raw
+// device pointers and a stream, checks its sizes on the host and returns a negative PE_ERR_* code for
+// a size it refuses.  Kernels never trap: a bad index or a wait that ran out is recorded in a status
+// word in global memory, the access is skipped, and the host reads the word after the step.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pe {
+
+constexpr int kPageTokens = 64;  // tokens per cache page (the unit in which the cache is handed out)
+
+// ---- status word -------------------------------------------------------------------------------
+// status[0]: first error code seen (0 = none); status[1..3]: details of that first error.
+enum StatusCode : int {
+  kStatusOk = 0,
+  kStatusTokenOutOfRange = 1,   // embedding: token id outside the table
+  kStatusPageOutOfRange = 2,    // cache: page table entry outside the pool
+  kStatusPositionOutOfRange = 3,// position beyond the tables or the page table
+  kStatusWaitTimedOut = 4,      // a bounded wait (mbarrier / TMA / MMA commit) ran out
+  kStatusSlotOutOfRange = 5,
+};
+
+__device__ __forceinline__ void report(int* status, int code, int a = 0, int b = 0, int c = 0) {
+  if (status == nullptr) return;
+  if (atomicCAS(status, 0, code) == 0) {
+    status[1] = a;
+    status[2] = b;
+    status[3] = c;
+  }
+}
+
+// ---- element conversion ----------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// ---- reductions --------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum in a fixed tree order (deterministic); `scratch` holds at least 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (lane < nwarps) ? scratch[lane] : 0.f;
+  r = warp_sum(r);
+  return r;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
+  r = warp_max(r);
+  return r;
+}
+
+}  // namespace pe
+
+// ---- error codes of the extern "C" launchers (negative; CUDA runtime errors are returned positive)
+#define PE_OK 0
+#define PE_ERR_UNSUPPORTED_SIZE (-1)
+#define PE_ERR_BAD_ARGUMENT (-2)
+#define PE_ERR_UNSUPPORTED_DTYPE (-3)
+
+// dtype tags of the C interface
+#define PE_F32 0
+#define PE_BF16 1
+
+#define PE_LAUNCH_CHECK()                         \
+  do {                                            \
+    cudaError_t e__ = cudaGetLastError();         \
+    if (e__ != cudaSuccess) return (int)e__;      \
+  } while (0)

@@ -1,0 +1,170 @@
+// Per-head q/k RMSNorm, rotary position encoding and the append of k, v to the paged cache, in one
+// pass over the fused q|k|v projection; and the small kernel that expands the batch description
+// into per-token sequence index and position.
+//
+// Reference formulas: q/k-norm over head_dim before RoPE, not on v (pygguf_engine/model.py:471-474);
+// split-half rotation of the first rotary_dim features with position = cached length + row
+// (pygguf_engine/model.py:232-241, 211-214); append at [P, P+S) (pygguf_engine/model.py:482-483);
+// positions read from device memory (pygguf_engine/kv_cache.py:1847-1852).
+#include "common.cuh"
+
+namespace pe {
+
+// token_seq[t] = index of the batch entry that token t belongs to; token_pos[t] = its position.
+__global__ void batch_expand_kernel(const int* __restrict__ seq_qstart, const int* __restrict__ seq_past,
+                                    int n_seqs, int* __restrict__ token_seq, int* __restrict__ token_pos) {
+  const int b = blockIdx.x;
+  if (b >= n_seqs) return;
+  const int q0 = seq_qstart[b], q1 = seq_qstart[b + 1], past = seq_past[b];
+  for (int t = q0 + threadIdx.x; t < q1; t += blockDim.x) {
+    token_seq[t] = b;
+    token_pos[t] = past + (t - q0);
+  }
+}
+
+struct RopeAppendArgs {
+  void* qkv;            // [n_tokens, ld]; q heads, then k heads, then v heads; q and k are rewritten in place
+  long long ld;
+  int n_tokens, n_heads, n_kv_heads, head_dim;
+  const float* q_norm_w;  // [head_dim] or null
+  const float* k_norm_w;  // [head_dim] or null
+  float eps;
+  const float* cos_table;  // [table_rows, rotary_dim/2] or null
+  const float* sin_table;
+  int rotary_dim, table_rows;
+  const int* token_seq;
+  const int* token_pos;
+  const int* seq_slot;
+  const int* page_table;   // [slots, table_stride]
+  int table_stride, num_pages;
+  void* k_pages;           // [num_pages, n_kv_heads, 64, head_dim]
+  void* v_pages;
+  int write_cache;
+  int* status;
+};
+
+template <typename T>
+__global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+  const int total_heads = a.n_heads + 2 * a.n_kv_heads;
+  if (t >= a.n_tokens || head >= total_heads) return;
+  const int d = a.head_dim;
+  T* row = (T*)a.qkv + (size_t)t * a.ld + (size_t)head * d;
+  const bool is_q = head < a.n_heads;
+  const bool is_k = !is_q && head < a.n_heads + a.n_kv_heads;
+  const int kv_head = is_q ? -1 : (is_k ? head - a.n_heads : head - a.n_heads - a.n_kv_heads);
+  const int pos = a.token_pos[t];
+
+  // where this token's k/v row lies in the paged cache
+  T* cache_row = nullptr;
+  if (!is_q && a.write_cache) {
+    const int slot = a.seq_slot[a.token_seq[t]];
+    const int logical = pos / kPageTokens;
+    if (pos < 0 || logical >= a.table_stride) {
+      if (lane == 0) report(a.status, kStatusPositionOutOfRange, t, pos, a.table_stride * kPageTokens);
+    } else {
+      const int page = a.page_table[(size_t)slot * a.table_stride + logical];
+      if (page < 0 || page >= a.num_pages) {
+        if (lane == 0) report(a.status, kStatusPageOutOfRange, t, page, a.num_pages);
+      } else {
+        T* base = (T*)(is_k ? a.k_pages : a.v_pages);
+        cache_row = base + (((size_t)page * a.n_kv_heads + kv_head) * kPageTokens + (pos % kPageTokens)) * d;
+      }
+    }
+  }
+
+  if (!is_q && !is_k) {  // v: copy only
+    if (cache_row)
+      for (int c = lane; c < d; c += 32) cache_row[c] = row[c];
+    return;
+  }
+
+  const float* w = is_q ? a.q_norm_w : a.k_norm_w;
+  float inv = 1.f;
+  if (w) {
+    float ss = 0.f;
+    for (int c = lane; c < d; c += 32) {
+      const float x = to_f32<T>(row[c]);
+      ss += x * x;
+    }
+    ss = warp_sum(ss);
+    inv = rsqrtf(ss / (float)d + a.eps);
+  }
+  // Norm and rotation are one float32 computation: nothing is rounded between them (the reference
+  // rounds to its 16-bit type in between only because they are separate ops there).
+  auto normed = [&](int c) -> float {
+    float x = to_f32<T>(row[c]);
+    if (w) x = x * inv * w[c];
+    return x;
+  };
+  const int rot = a.cos_table ? a.rotary_dim : 0;
+  const int half = rot / 2;
+  if (rot > 0 && (pos < 0 || pos >= a.table_rows)) {
+    if (lane == 0) report(a.status, kStatusPositionOutOfRange, t, pos, a.table_rows);
+    return;
+  }
+  const float* cs = a.cos_table ? a.cos_table + (size_t)pos * half : nullptr;
+  const float* sn = a.sin_table ? a.sin_table + (size_t)pos * half : nullptr;
+  // rotated pairs (j, j + half): both are read before either is written
+  for (int j = lane; j < half; j += 32) {
+    const float x1 = normed(j), x2 = normed(j + half);
+    const float c = cs[j], s = sn[j];
+    const T o1 = from_f32<T>(x1 * c - x2 * s);
+    const T o2 = from_f32<T>(x2 * c + x1 * s);
+    row[j] = o1;
+    row[j + half] = o2;
+    if (cache_row) {
+      cache_row[j] = o1;
+      cache_row[j + half] = o2;
+    }
+  }
+  // features beyond rotary_dim pass through (normalised only)
+  for (int c = rot + lane; c < d; c += 32) {
+    const T o = from_f32<T>(normed(c));
+    row[c] = o;
+    if (cache_row) cache_row[c] = o;
+  }
+}
+
+}  // namespace pe
+
+extern "C" int pe_batch_expand(const int* seq_qstart, const int* seq_past, int n_seqs, int* token_seq, int* token_pos,
+                               cudaStream_t stream) {
+  if (n_seqs <= 0) return PE_OK;
+  pe::batch_expand_kernel<<<n_seqs, 128, 0, stream>>>(seq_qstart, seq_past, n_seqs, token_seq, token_pos);
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+extern "C" int pe_qk_norm_rope_append(int dtype, void* qkv, long long ld, int n_tokens, int n_heads, int n_kv_heads,
+                                      int head_dim, const float* q_norm_w, const float* k_norm_w, float eps,
+                                      const float* cos_table, const float* sin_table, int rotary_dim, int table_rows,
+                                      const int* token_seq, const int* token_pos, const int* seq_slot,
+                                      const int* page_table, int table_stride, int num_pages, void* k_pages,
+                                      void* v_pages, int write_cache, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return PE_OK;
+  if (head_dim <= 0 || n_heads <= 0 || n_kv_heads < 0) return PE_ERR_BAD_ARGUMENT;
+  if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return PE_ERR_UNSUPPORTED_SIZE;
+  if (ld < (long long)(n_heads + 2 * n_kv_heads) * head_dim) return PE_ERR_BAD_ARGUMENT;
+  pe::RopeAppendArgs a;
+  a.qkv = qkv; a.ld = ld; a.n_tokens = n_tokens; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim;
+  a.q_norm_w = q_norm_w; a.k_norm_w = k_norm_w; a.eps = eps;
+  a.cos_table = cos_table; a.sin_table = sin_table; a.rotary_dim = rotary_dim; a.table_rows = table_rows;
+  a.token_seq = token_seq; a.token_pos = token_pos; a.seq_slot = seq_slot;
+  a.page_table = page_table; a.table_stride = table_stride; a.num_pages = num_pages;
+  a.k_pages = k_pages; a.v_pages = v_pages; a.write_cache = write_cache; a.status = status;
+  const int warps = 4;
+  const int total_heads = n_heads + 2 * n_kv_heads;
+  dim3 grid(n_tokens, (total_heads + warps - 1) / warps);
+  if (grid.y > 65535) return PE_ERR_UNSUPPORTED_SIZE;
+  if (dtype == PE_F32)
+    pe::qk_norm_rope_append_kernel<float><<<grid, warps * 32, 0, stream>>>(a);
+  else if (dtype == PE_BF16)
+    pe::qk_norm_rope_append_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(a);
+  else
+    return PE_ERR_UNSUPPORTED_DTYPE;
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}

@@ -1,0 +1,121 @@
+"""The step function: a batch of sequences that started together, from the cache, to logits.
+
+``ModelRunner.step(entries)`` runs exactly the tokens it is given, as one batch: for each entry the
+tokens follow what that entry's slot already holds.  Prompts of unequal lengths go in one step;
+later steps bring one token per live sequence.  Logits come back only for the wanted positions.
+Nothing is padded in the eager path; the CUDA-graph path for one-token steps replays a graph
+captured for exactly that number of sequences, with slots and lengths read from device memory
+(the reference feeds its decode graphs the position the same way, pygguf_engine/model.py:197-209,
+1743-1872).  Generation, the Python entry point and trace replay all go through this one function.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache import PagedCache
+from ..kernels import ops
+from .batch import BufferPool, StepContext, StepEntry
+from .model import DecoderModel
+
+
+class _DecodeGraph:
+    def __init__(self, graph, ctx: StepContext, logits: torch.Tensor, pool: BufferPool) -> None:
+        self.graph = graph
+        self.ctx = ctx
+        self.logits = logits
+        self.pool = pool
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: PagedCache, *, cuda_graphs: bool = True) -> None:
+        self.model = model
+        self.cache = cache
+        self.runtime = model.runtime
+        self.pool = BufferPool(self.runtime.device)
+        self.cuda_graphs = bool(cuda_graphs) and self.runtime.is_cuda
+        self._graphs: Dict[int, _DecodeGraph] = {}
+        self.steps_run = 0
+        self.kernel_launch_estimate = 0
+
+    # ---- slots -------------------------------------------------------------------------
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    # ---- the step ------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry], check: bool = True) -> torch.Tensor:
+        """Logits (float32, ``[wanted positions in entry order, vocab]``) after feeding each entry's
+        tokens.  The returned tensor may be overwritten by the next step."""
+        entries = list(entries)
+        if not entries:
+            raise ValueError("a step needs at least one sequence")
+        seen = set()
+        pasts: List[int] = []
+        for e in entries:
+            if e.slot in seen:
+                raise ValueError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if len(e.tokens) == 0:
+                raise ValueError(f"slot {e.slot} brings no token in this step")
+            pasts.append(self.cache.length(e.slot))
+        # make room first: a failure here leaves the cache as it was
+        for e, past in zip(entries, pasts):
+            self.cache.reserve(e.slot, past + len(e.tokens))
+        ints, n_tokens, n_want = StepContext.pack_meta(entries, pasts)
+        n_seqs = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        decode = all(q == 1 for q in q_lens)
+        host = torch.tensor(ints, dtype=torch.int32)
+        if decode and self.cuda_graphs and n_want == n_seqs and all(tuple(e.want) == (0,) for e in entries):
+            logits = self._step_graph(host, n_seqs)
+        else:
+            ctx = StepContext(self.runtime, self.pool, n_tokens=n_tokens, n_seqs=n_seqs, max_q=max(q_lens),
+                              decode=decode, max_kv_len=max(p + q for p, q in zip(pasts, q_lens)), n_want=n_want)
+            ctx.meta.copy_(host)
+            ops.batch_expand(ctx.seq_qstart, ctx.seq_past, n_seqs, ctx.token_seq, ctx.token_pos)
+            logits = self.model.forward(ctx, self.cache)
+        for e, past in zip(entries, pasts):
+            self.cache.commit(e.slot, past + len(e.tokens))
+        self.steps_run += 1
+        if check:
+            self.runtime.raise_on_status()
+        return logits
+
+    def _step_graph(self, host_meta: torch.Tensor, n_seqs: int) -> torch.Tensor:
+        g = self._graphs.get(n_seqs)
+        if g is None:
+            g = self._capture(host_meta, n_seqs)
+        else:
+            g.ctx.meta.copy_(host_meta)
+            g.graph.replay()
+        return g.logits
+
+    def _capture(self, host_meta: torch.Tensor, n_seqs: int) -> _DecodeGraph:
+        """Capture one decode step for exactly ``n_seqs`` sequences.  The capture itself runs the
+        step once eagerly first (warm-up: library handles, kernel attributes), then records it."""
+        pool = BufferPool(self.runtime.device)
+        ctx = StepContext(self.runtime, pool, n_tokens=n_seqs, n_seqs=n_seqs, max_q=1, decode=True,
+                          max_kv_len=self.cache.max_seq_len, n_want=n_seqs)
+        ctx.meta.copy_(host_meta)
+        stream = torch.cuda.Stream(device=self.runtime.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            ops.batch_expand(ctx.seq_qstart, ctx.seq_past, n_seqs, ctx.token_seq, ctx.token_pos)
+            self.model.forward(ctx, self.cache)  # warm-up; writes the same cache rows the capture run will
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize(self.runtime.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            ops.batch_expand(ctx.seq_qstart, ctx.seq_past, n_seqs, ctx.token_seq, ctx.token_pos)
+            logits = self.model.forward(ctx, self.cache)
+        graph.replay()
+        g = _DecodeGraph(graph, ctx, logits, pool)
+        self._graphs[n_seqs] = g
+        return g
+
+    def workspace_bytes(self) -> int:
+        return self.pool.nbytes() + sum(g.pool.nbytes() for g in self._graphs.values())

@@ -1,0 +1,128 @@
+"""Tensor-level wrappers of the CUDA entry points.  Every op requires CUDA tensors."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .lib import PE_BF16, PE_F32, KernelError, check, library
+
+
+def dtype_tag(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return PE_F32
+    if dtype == torch.bfloat16:
+        return PE_BF16
+    raise KernelError(f"unsupported dtype {dtype}: the kernels run in float32 or bfloat16")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("the kernels of this package run on CUDA tensors only; got a CPU tensor")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    _need(ids.dtype == torch.int32 and out.dtype == torch.float32, "embed_gather: ids int32, out float32")
+    _need(table.is_contiguous() and out.is_contiguous() and ids.is_contiguous(), "embed_gather: contiguous tensors")
+    n, hidden = out.shape
+    check(library().pe_embed_gather(dtype_tag(table.dtype), _ptr(table), _ptr(ids), _ptr(out), n, hidden,
+                                    table.shape[0], _ptr(status), _stream()), "embed_gather")
+
+
+def rmsnorm_residual(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                     eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """``out = rmsnorm(residual (+ delta)) * weight``; see csrc/rmsnorm.cu for the two modes."""
+    _need(residual.dtype == torch.float32 and weight.dtype == torch.float32, "rmsnorm: stream and weight float32")
+    _need(residual.is_contiguous() and out.is_contiguous(), "rmsnorm: contiguous tensors")
+    if delta is not None:
+        _need(delta.dtype == out.dtype and delta.is_contiguous() and delta.shape == residual.shape,
+              "rmsnorm: delta must match the stream's shape and the output dtype")
+    dim = residual.shape[-1]
+    n_rows = out.shape[0]
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.numel() == n_rows, "rmsnorm: rows int32, one per output row")
+    else:
+        _need(n_rows == residual.shape[0], "rmsnorm: output rows must match the stream")
+    check(library().pe_rmsnorm_residual(dtype_tag(out.dtype), _ptr(residual), _ptr(delta), _ptr(weight), _ptr(out),
+                                        _ptr(rows), n_rows, dim, float(eps), _stream()), "rmsnorm_residual")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float) -> None:
+    _need(x.is_contiguous() and out.is_contiguous() and weight.dtype == torch.float32, "rmsnorm: contiguous, weight f32")
+    dim = x.shape[-1]
+    check(library().pe_rmsnorm(dtype_tag(x.dtype), _ptr(x), _ptr(weight), _ptr(out), x.numel() // dim, dim, float(eps),
+                               _stream()), "rmsnorm")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    _need(gate_up.is_contiguous() and out.is_contiguous(), "silu_mul: contiguous tensors")
+    n, two_i = gate_up.shape
+    _need(two_i == 2 * out.shape[1] and out.shape[0] == n and out.dtype == gate_up.dtype, "silu_mul: shapes")
+    check(library().pe_silu_mul(dtype_tag(gate_up.dtype), _ptr(gate_up), _ptr(out), n, out.shape[1], _stream()), "silu_mul")
+
+
+def batch_expand(seq_qstart: torch.Tensor, seq_past: torch.Tensor, n_seqs: int, token_seq: torch.Tensor,
+                 token_pos: torch.Tensor) -> None:
+    check(library().pe_batch_expand(_ptr(seq_qstart), _ptr(seq_past), n_seqs, _ptr(token_seq), _ptr(token_pos),
+                                    _stream()), "batch_expand")
+
+
+def qk_norm_rope_append(qkv: torch.Tensor, n_tokens: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                        q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
+                        cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
+                        token_seq: torch.Tensor, token_pos: torch.Tensor, seq_slot: torch.Tensor,
+                        page_table: Optional[torch.Tensor], num_pages: int, k_pages: Optional[torch.Tensor],
+                        v_pages: Optional[torch.Tensor], write_cache: bool, status: torch.Tensor) -> None:
+    _need(qkv.stride(-1) == 1, "qk_norm_rope_append: rows of qkv must be contiguous")
+    table_rows = 0 if cos is None else cos.shape[0]
+    check(library().pe_qk_norm_rope_append(
+        dtype_tag(qkv.dtype), _ptr(qkv), qkv.stride(0), n_tokens, n_heads, n_kv_heads, head_dim,
+        _ptr(q_norm_w), _ptr(k_norm_w), float(eps), _ptr(cos), _ptr(sin), rotary_dim if cos is not None else 0,
+        table_rows, _ptr(token_seq), _ptr(token_pos), _ptr(seq_slot), _ptr(page_table),
+        0 if page_table is None else page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages),
+        1 if write_cache else 0, _ptr(status), _stream()), "qk_norm_rope_append")
+
+
+def attention_generic_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, max_splits: int) -> int:
+    return int(library().pe_attention_generic_scratch_floats(n_seqs, n_heads, head_dim, max_splits))
+
+
+def attention_generic(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_q: int, n_heads: int,
+                      n_kv_heads: int, head_dim: int, scale: float, window: int, seq_qstart: torch.Tensor,
+                      seq_past: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int,
+                      k_pages: torch.Tensor, v_pages: torch.Tensor, scratch: Optional[torch.Tensor], split_keys: int,
+                      max_splits: int, status: torch.Tensor) -> None:
+    _need(q.stride(-1) == 1 and out.stride(-1) == 1, "attention: rows must be contiguous")
+    _need(q.dtype == out.dtype == k_pages.dtype, "attention: q, out and the cache must share a dtype")
+    check(library().pe_attention_generic(
+        dtype_tag(q.dtype), 1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), n_seqs, max_q,
+        n_heads, n_kv_heads, head_dim, float(scale), int(window), _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot),
+        _ptr(page_table), page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages), _ptr(scratch), split_keys,
+        max_splits, _ptr(status), _stream()), "attention_generic")
+
+
+def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float, seed: int,
+           row_request: torch.Tensor, row_step: torch.Tensor, out_tokens: torch.Tensor) -> None:
+    _need(logits.dtype == torch.float32 and logits.stride(-1) == 1, "sample: float32 logits with contiguous rows")
+    n, vocab = logits.shape
+    check(library().pe_sample(_ptr(logits), logits.stride(0), n, vocab, float(temperature), int(top_k), float(top_p),
+                              float(min_p), int(seed) & ((1 << 64) - 1), _ptr(row_request), _ptr(row_step),
+                              _ptr(out_tokens), _stream()), "sample")
+
+
+def repetition_penalty(logits: torch.Tensor, recent: torch.Tensor, recent_count: torch.Tensor, penalty: float) -> None:
+    n, vocab = logits.shape
+    check(library().pe_repetition_penalty(_ptr(logits), logits.stride(0), n, vocab, _ptr(recent), recent.shape[1],
+                                          _ptr(recent_count), float(penalty), _stream()), "repetition_penalty")

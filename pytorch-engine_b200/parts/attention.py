@@ -1,0 +1,111 @@
+"""Grouped-query softmax attention over the paged cache, with optional per-head q/k RMSNorm,
+optional rotary position encoding and an optional sliding window.
+
+Order of operations (pygguf_engine/model.py:462-496): fused q|k|v projection, head split,
+q/k-norm over head_dim (before RoPE, not on v), RoPE at position = cached length + row, append of
+k, v to the cache, attention with scale ``1/sqrt(head_dim)`` unless the plan gives another
+(pygguf_engine/model.py:281-284), merge heads, output projection.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from ..kernels import ops
+from .linear import fuse_rows
+from .registry import register
+from .spec import CacheRequest, WeightDecl
+
+SPLIT_KEYS = 256  # keys per partial result in decode; a property of the sequence, not of the batch
+
+
+@register("mixer", "attention")
+class GQAttention:
+    """params: ``hidden``, ``n_heads``, ``n_kv_heads``, ``head_dim``, ``qk_norm`` (bool), ``eps``,
+    ``scale`` (None: 1/sqrt(head_dim)), ``window`` (None: all keys), ``position`` (name of a position
+    encoding of the plan, or None).  weights: ``q_proj, k_proj, v_proj, o_proj`` and, with qk_norm,
+    ``q_norm, k_norm``."""
+
+    @classmethod
+    def weight_decls(cls, params) -> Dict[str, WeightDecl]:
+        h, nh, nkv, d = (int(params[k]) for k in ("hidden", "n_heads", "n_kv_heads", "head_dim"))
+        decls = {
+            "q_proj": WeightDecl((nh * d, h)),
+            "k_proj": WeightDecl((nkv * d, h)),
+            "v_proj": WeightDecl((nkv * d, h)),
+            "o_proj": WeightDecl((h, nh * d)),
+        }
+        if params.get("qk_norm", False):
+            decls["q_norm"] = WeightDecl((d,), "norm")
+            decls["k_norm"] = WeightDecl((d,), "norm")
+        return decls
+
+    @classmethod
+    def cache_request(cls, params) -> Optional[CacheRequest]:
+        return CacheRequest(kind="kv", kv_heads=int(params["n_kv_heads"]), head_dim=int(params["head_dim"]),
+                            window=params.get("window"))
+
+    def __init__(self, params, weights, runtime, positions=None) -> None:
+        self.runtime = runtime
+        self.hidden = int(params["hidden"])
+        self.n_heads = int(params["n_heads"])
+        self.n_kv_heads = int(params["n_kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError("n_heads must be a multiple of n_kv_heads")
+        if self.head_dim > 512:
+            raise ValueError(f"head_dim {self.head_dim} is beyond what the attention kernels take (<= 512)")
+        self.eps = float(params.get("eps", 1e-6))
+        scale = params.get("scale")
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.window = int(params["window"]) if params.get("window") else 0
+        self.qkv = fuse_rows(runtime, [weights["q_proj"], weights["k_proj"], weights["v_proj"]])
+        self.o_proj = runtime.adopt(weights["o_proj"])
+        self.q_norm = self.k_norm = None
+        if params.get("qk_norm", False):
+            self.q_norm = runtime.adopt(weights["q_norm"], torch.float32)
+            self.k_norm = runtime.adopt(weights["k_norm"], torch.float32)
+        self.position = None
+        name = params.get("position")
+        if name is not None:
+            self.position = (positions or {})[name]
+            if not getattr(self.position, "fusable_rotary", False):
+                raise ValueError(f"position encoding {name!r} cannot be fused into attention (needs tables())")
+        self.qkv_dim = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
+
+    def forward(self, x: torch.Tensor, ctx, view, writes_cache: bool = True) -> torch.Tensor:
+        rt = self.runtime
+        n = x.shape[0]
+        qkv = ctx.buffer("attn.qkv", (n, self.qkv_dim), rt.dtype)
+        rt.linear(x, self.qkv, out=qkv)
+        cos = sin = None
+        rotary_dim = 0
+        if self.position is not None:
+            cos, sin, rotary_dim = self.position.tables()
+        ops.qk_norm_rope_append(
+            qkv, n, self.n_heads, self.n_kv_heads, self.head_dim, self.q_norm, self.k_norm, self.eps, cos, sin,
+            rotary_dim, ctx.token_seq, ctx.token_pos, ctx.seq_slot, view.page_table, view.num_pages, view.k_pages,
+            view.v_pages, writes_cache, rt.status)
+        out = ctx.buffer("attn.out", (n, self.n_heads * self.head_dim), rt.dtype)
+        self.attend(qkv, out, ctx, view)
+        delta = ctx.buffer("attn.delta", (n, self.hidden), rt.dtype)
+        rt.linear(out, self.o_proj, out=delta)
+        return delta
+
+    def attend(self, q: torch.Tensor, out: torch.Tensor, ctx, view) -> None:
+        """Attention of the step's queries (the first ``n_heads*head_dim`` features of each row of
+        ``q``) over the cache of their sequences."""
+        scratch = None
+        max_splits = 0
+        if ctx.decode:
+            max_splits = ctx.max_splits(SPLIT_KEYS)
+            scratch = ctx.buffer(
+                "attn.scratch",
+                (ops.attention_generic_scratch_floats(ctx.n_seqs, self.n_heads, self.head_dim, max_splits),),
+                torch.float32)
+        ops.attention_generic(
+            ctx.decode, q, out, ctx.n_seqs, ctx.max_q, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
+            self.window, ctx.seq_qstart, ctx.seq_past, ctx.seq_slot, view.page_table, view.num_pages, view.k_pages,
+            view.v_pages, scratch, SPLIT_KEYS, max_splits, self.runtime.status)

@@ -1,0 +1,86 @@
+"""What parts share at run time: device, run dtype, the status word, and the matrix product.
+
+``Runtime.linear`` is the one place where ``y = x W^T`` is computed.  The reference computes its
+unquantised linears with a library call (``F.linear``, pygguf_engine/quant_kernels.py:1836); here
+the library product (cuBLAS through ``torch.mm``) stands wherever the package's own tensor-core
+kernels do not take the shape, and the float32 mode always runs in true float32 (TF32 is switched
+off around the call).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..kernels import KernelError
+
+STATUS_MESSAGES = {
+    1: "a token id is outside the embedding table (token row {0}, id {1}, vocabulary {2})",
+    2: "a cache page number is outside the pool ({0}, page {1}, {2})",
+    3: "a position is beyond the position tables or the page table (token {0}, position {1}, limit {2})",
+    4: "a bounded wait inside a kernel ran out (where {0}, detail {1}, {2})",
+    5: "a slot number is outside the cache ({0}, {1}, {2})",
+}
+
+
+class Runtime:
+    def __init__(self, device, dtype: torch.dtype) -> None:
+        self.device = torch.device(device)
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise KernelError(f"run dtype must be float32 or bfloat16, got {dtype}")
+        self.dtype = dtype
+        self.is_cuda = self.device.type == "cuda"
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._adopted: Dict[Tuple[int, torch.dtype], torch.Tensor] = {}
+        self.gemm_backend = None  # set by kernels that take over matrix products (see parts/linear.py)
+
+    # ---- weights -------------------------------------------------------------------------
+    def adopt(self, tensor: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """The tensor on the run device in ``dtype`` (default: the run dtype), converted once even if
+        several parts use it (tied embedding and output head share one copy)."""
+        dtype = dtype or self.dtype
+        key = (id(tensor), dtype)
+        got = self._adopted.get(key)
+        if got is None:
+            got = tensor.to(device=self.device, dtype=dtype).contiguous()
+            self._adopted[key] = got
+        return got
+
+    def forget_adopted(self) -> None:
+        self._adopted.clear()
+
+    # ---- status word -----------------------------------------------------------------------
+    def raise_on_status(self) -> None:
+        """Read the kernels' status word (one small device-to-host copy) and raise if it is set."""
+        s = self.status.tolist()
+        if s[0] != 0:
+            self.status.zero_()
+            msg = STATUS_MESSAGES.get(s[0], "kernel status {0}").format(*s[1:])
+            raise KernelError(f"a kernel reported an error during the step: {msg}")
+
+    # ---- matrix product ----------------------------------------------------------------------
+    def linear(self, x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
+               out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``x [M, K] @ weight [N, K]^T -> [M, N]``."""
+        if not self.is_cuda:
+            raise KernelError("this package computes on a CUDA device only; there is no CPU path")
+        if self.gemm_backend is not None:
+            y = self.gemm_backend(x, weight, out, out_dtype)
+            if y is not None:
+                return y
+        if x.dtype == torch.float32:
+            prev = torch.backends.cuda.matmul.allow_tf32
+            if prev:
+                torch.backends.cuda.matmul.allow_tf32 = False
+            try:
+                return torch.mm(x, weight.t(), out=out) if out is not None else torch.mm(x, weight.t())
+            finally:
+                if prev:
+                    torch.backends.cuda.matmul.allow_tf32 = True
+        if out_dtype is not None and out_dtype != x.dtype:
+            y = torch.mm(x, weight.t(), out_dtype=out_dtype)
+            if out is not None:
+                out.copy_(y)
+                return out
+            return y
+        return torch.mm(x, weight.t(), out=out) if out is not None else torch.mm(x, weight.t())

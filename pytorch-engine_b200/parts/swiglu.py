@@ -1,0 +1,40 @@
+"""SwiGLU feed-forward: ``down(silu(gate(x)) * up(x))`` with gate|up as one product
+(pygguf_engine/model.py:839-846, pygguf_engine/quant_kernels.py:1467-1472)."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..kernels import ops
+from .linear import fuse_rows
+from .registry import register
+from .spec import WeightDecl
+
+
+@register("feed_forward", "swiglu")
+class SwiGLU:
+    """params: ``hidden``, ``intermediate``.  weights: ``gate_proj, up_proj [I, H]``, ``down_proj [H, I]``."""
+
+    @classmethod
+    def weight_decls(cls, params) -> Dict[str, WeightDecl]:
+        h, i = int(params["hidden"]), int(params["intermediate"])
+        return {"gate_proj": WeightDecl((i, h)), "up_proj": WeightDecl((i, h)), "down_proj": WeightDecl((h, i))}
+
+    def __init__(self, params, weights, runtime) -> None:
+        self.runtime = runtime
+        self.hidden = int(params["hidden"])
+        self.intermediate = int(params["intermediate"])
+        self.gate_up = fuse_rows(runtime, [weights["gate_proj"], weights["up_proj"]])
+        self.down = runtime.adopt(weights["down_proj"])
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        rt = self.runtime
+        n = x.shape[0]
+        gu = ctx.buffer("ffn.gate_up", (n, 2 * self.intermediate), rt.dtype)
+        rt.linear(x, self.gate_up, out=gu)
+        act = ctx.buffer("ffn.act", (n, self.intermediate), rt.dtype)
+        ops.silu_mul(gu, act)
+        delta = ctx.buffer("ffn.delta", (n, self.hidden), rt.dtype)
+        rt.linear(act, self.down, out=delta)
+        return delta

@@ -1,0 +1,39 @@
+"""The device sampler: float32 logits rows -> one token id per row (see csrc/sampling.cu)."""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..kernels import ops
+from .params import SamplingParams
+
+RECENT_WINDOW = 256  # the reference penalises the unique ids among the last 256 tokens (engine.py:94)
+
+
+class Sampler:
+    def __init__(self, device) -> None:
+        self.device = torch.device(device)
+
+    def sample(self, logits: torch.Tensor, params: SamplingParams, seed: int, requests: Sequence[int],
+               steps: Sequence[int], recent: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
+        """One token per row of ``logits``.  ``requests[r]`` and ``steps[r]`` key row r's random
+        numbers (the request's index and how many tokens it has drawn so far); ``recent[r]`` is the
+        row's token history for the repetition penalty."""
+        n = logits.shape[0]
+        if n == 0:
+            return []
+        if params.repetition_penalty != 1.0 and recent is not None:
+            logits = logits.clone()
+            rec = torch.zeros((n, RECENT_WINDOW), dtype=torch.int32)
+            cnt = torch.zeros((n,), dtype=torch.int32)
+            for r, hist in enumerate(recent):
+                tail = list(hist)[-RECENT_WINDOW:]
+                cnt[r] = len(tail)
+                if tail:
+                    rec[r, :len(tail)] = torch.tensor(tail, dtype=torch.int32)
+            ops.repetition_penalty(logits, rec.to(self.device), cnt.to(self.device), params.repetition_penalty)
+        meta = torch.tensor([list(requests), list(steps)], dtype=torch.int32).to(self.device)
+        out = torch.empty((n,), dtype=torch.int32, device=self.device)
+        ops.sample(logits, params.temperature, params.top_k, params.top_p, params.min_p, seed, meta[0], meta[1], out)
+        return out.tolist()

@@ -1,0 +1,151 @@
+"""Cache bookkeeping on the CPU: no slot or page lost, held twice or freed twice."""
+import random
+
+import pytest
+import torch
+
+
+def _cache(pe, max_tokens=64 * 12, max_slots=4, max_seq_len=512, window=None, with_state=False):
+    CR = pe.parts.CacheRequest
+    reqs = {0: CR("kv", kv_heads=2, head_dim=16), 1: CR("kv", kv_heads=2, head_dim=16),
+            2: CR("kv", kv_heads=2, head_dim=16, window=window) if window else CR("kv", kv_heads=2, head_dim=16)}
+    if with_state:
+        reqs[3] = CR("state", state_shapes=(("acc", (3, 5), "float32"),))
+    return pe.cache.PagedCache(reqs, max_tokens=max_tokens, max_slots=max_slots, max_seq_len=max_seq_len,
+                               dtype=torch.float32, device="cpu")
+
+
+def test_groups_have_storage_of_their_own(pe):
+    c = _cache(pe, window=100, with_state=True)
+    kinds = [(g.request.kind, g.request.window, g.entries) for g in c.groups]
+    assert kinds == [("kv", None, [0, 1]), ("kv", 100, [2]), ("state", None, [3])]
+    assert c.groups[0].storage.shape == (2, 2, 12, 2, 64, 16)
+    assert c.groups[1].storage.shape == (1, 2, 12, 2, 64, 16)
+    assert c.groups[0].storage.data_ptr() != c.groups[1].storage.data_ptr()
+    assert c.view(1).index == 1 and c.view(2).index == 0 and c.view(2).window == 100
+    assert c.view(3).state("acc").shape == (4, 3, 5)
+
+
+def test_slots_are_reused_and_never_held_twice(pe):
+    c = _cache(pe)
+    a, b = c.alloc_slot(), c.alloc_slot()
+    assert a != b
+    c.free_slot(a)
+    assert c.alloc_slot() == a  # the slot just given back is used again at once
+    c.alloc_slot(), c.alloc_slot()
+    with pytest.raises(pe.cache.CacheFull):
+        c.alloc_slot()
+    c.check()
+
+
+def test_double_free_and_unknown_slot(pe):
+    c = _cache(pe)
+    s = c.alloc_slot()
+    c.free_slot(s)
+    with pytest.raises(pe.cache.CacheBookkeepingError):
+        c.free_slot(s)
+    with pytest.raises(pe.cache.CacheBookkeepingError):
+        c.free_slot(3)
+    pool = pe.cache.NumberPool(3)
+    n = pool.take()
+    pool.give_back(n)
+    with pytest.raises(pe.cache.CacheBookkeepingError):
+        pool.give_back(n)
+    with pytest.raises(pe.cache.CacheBookkeepingError):
+        pool.give_back(7)
+
+
+def test_pages_follow_lengths(pe):
+    c = _cache(pe)
+    s = c.alloc_slot()
+    c.reserve(s, 5); c.commit(s, 5)
+    assert len(c.groups[0].pages_of_slot[s]) == 1 and c.free_pages() == 11
+    c.reserve(s, 64); c.commit(s, 64)
+    assert len(c.groups[0].pages_of_slot[s]) == 1
+    c.reserve(s, 65); c.commit(s, 65)
+    assert len(c.groups[0].pages_of_slot[s]) == 2
+    table = c.groups[0].page_table[s, :2].tolist()
+    assert table == c.groups[0].pages_of_slot[s]
+    c.free_slot(s)
+    assert c.free_pages() == 12
+    c.check()
+
+
+def test_full_cache_raises_and_changes_nothing(pe):
+    c = _cache(pe, max_tokens=64 * 3)
+    a, b = c.alloc_slot(), c.alloc_slot()
+    c.reserve(a, 128); c.commit(a, 128)
+    before = (c.free_pages(), list(c.groups[0].pages_of_slot[b]))
+    with pytest.raises(pe.cache.CacheFull):
+        c.reserve(b, 129)
+    assert (c.free_pages(), list(c.groups[0].pages_of_slot[b])) == before
+    with pytest.raises(pe.cache.CacheFull):
+        c.reserve(a, 513)  # beyond the longest sequence
+    c.check()
+
+
+def test_window_group_gives_pages_back(pe):
+    c = _cache(pe, window=70, max_tokens=64 * 12)
+    s = c.alloc_slot()
+    c.reserve(s, 300); c.commit(s, 300)
+    full, win = c.groups[0], c.groups[1]
+    assert all(p >= 0 for p in full.pages_of_slot[s]) and len(full.pages_of_slot[s]) == 5
+    # the next query sits at 300 and sees keys 231..300: pages 0..2 (positions < 192) are gone
+    assert [p >= 0 for p in win.pages_of_slot[s]] == [False, False, False, True, True]
+    assert win.pool.held_count == 2 and full.pool.held_count == 5
+    c.check()
+    c.free_slot(s)
+    assert win.pool.held_count == 0 and full.pool.held_count == 0
+    c.check()
+
+
+def test_state_is_zero_for_a_new_sequence(pe):
+    c = _cache(pe, with_state=True)
+    s = c.alloc_slot()
+    c.view(3).state("acc")[s] += 4.0
+    c.free_slot(s)
+    s2 = c.alloc_slot()
+    assert s2 == s and float(c.view(3).state("acc")[s2].abs().sum()) == 0.0
+
+
+def test_truncate(pe):
+    c = _cache(pe)
+    s = c.alloc_slot()
+    c.reserve(s, 200); c.commit(s, 200)
+    c.truncate(s, 70)
+    assert c.length(s) == 70 and len(c.groups[0].pages_of_slot[s]) == 2
+    c.check()
+    cw = _cache(pe, window=70)
+    s = cw.alloc_slot()
+    cw.reserve(s, 10); cw.commit(s, 10)
+    with pytest.raises(pe.cache.CacheBookkeepingError):
+        cw.truncate(s, 5)
+
+
+def test_random_traffic_keeps_the_books(pe):
+    rng = random.Random(0)
+    c = _cache(pe, max_tokens=64 * 40, max_slots=6, max_seq_len=700, window=90)
+    live = {}
+    for _ in range(600):
+        op = rng.random()
+        if op < 0.3 and len(live) < 6:
+            live[c.alloc_slot()] = 0
+        elif op < 0.5 and live:
+            s = rng.choice(list(live))
+            c.free_slot(s)
+            del live[s]
+        elif live:
+            s = rng.choice(list(live))
+            new = min(700, live[s] + rng.choice([1, 1, 1, 17, 64, 130]))
+            try:
+                c.reserve(s, new)
+            except pe.cache.CacheFull:
+                continue
+            c.commit(s, new)
+            live[s] = new
+        c.check()
+        assert sorted(live) == c.live_slots
+    for s in list(live):
+        c.free_slot(s)
+    c.check()
+    assert all(g.pool.held_count == 0 for g in c.groups if g.pool)
