@@ -167,7 +167,7 @@ class PagedCache:
 
     def free_pages(self) -> int:
         kv = [g.pool.free_count for g in self.groups if g.pool is not None]
-        return min(kv) if kv else 0
+        return min(kv) if kv else (1 << 30)  # nothing is paged: no page limit
 
     # ---- growing a sequence ----------------------------------------------------------------
     def reserve(self, slot: int, new_length: int) -> None:

@@ -21,11 +21,12 @@ from .model import DecoderModel
 
 
 class _DecodeGraph:
-    def __init__(self, graph, ctx: StepContext, logits: torch.Tensor, pool: BufferPool) -> None:
+    def __init__(self, graph, ctx: StepContext, logits: torch.Tensor, pool: BufferPool, launches: int) -> None:
         self.graph = graph
         self.ctx = ctx
         self.logits = logits
         self.pool = pool
+        self.launches = launches  # kernels of this package recorded in the graph
 
 
 class ModelRunner:
@@ -92,6 +93,7 @@ class ModelRunner:
         else:
             g.ctx.meta.copy_(host_meta)
             g.graph.replay()
+            ops.count_replay(g.launches)
         return g.logits
 
     def _capture(self, host_meta: torch.Tensor, n_seqs: int) -> _DecodeGraph:
@@ -109,11 +111,13 @@ class ModelRunner:
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize(self.runtime.device)
         graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
         with torch.cuda.graph(graph, stream=stream):
             ops.batch_expand(ctx.seq_qstart, ctx.seq_past, n_seqs, ctx.token_seq, ctx.token_pos)
             logits = self.model.forward(ctx, self.cache)
+        launches = ops.launch_count() - before
         graph.replay()
-        g = _DecodeGraph(graph, ctx, logits, pool)
+        g = _DecodeGraph(graph, ctx, logits, pool, launches)
         self._graphs[n_seqs] = g
         return g
 

@@ -28,6 +28,24 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+# How many kernels of this library were launched (a replayed CUDA graph counts its captured kernels
+# through ``count_replay``); benchmarks report it.
+_LAUNCHES = 0
+
+
+def _count(n: int = 1) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
+def launch_count() -> int:
+    return _LAUNCHES
+
+
+def count_replay(n: int) -> None:
+    _count(n)
+
+
 def _need(cond: bool, msg: str) -> None:
     if not cond:
         raise KernelError(msg)
@@ -39,6 +57,7 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stat
     n, hidden = out.shape
     check(library().pe_embed_gather(dtype_tag(table.dtype), _ptr(table), _ptr(ids), _ptr(out), n, hidden,
                                     table.shape[0], _ptr(status), _stream()), "embed_gather")
+    _count(1)
 
 
 def rmsnorm_residual(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
@@ -57,6 +76,7 @@ def rmsnorm_residual(residual: torch.Tensor, delta: Optional[torch.Tensor], weig
         _need(n_rows == residual.shape[0], "rmsnorm: output rows must match the stream")
     check(library().pe_rmsnorm_residual(dtype_tag(out.dtype), _ptr(residual), _ptr(delta), _ptr(weight), _ptr(out),
                                         _ptr(rows), n_rows, dim, float(eps), _stream()), "rmsnorm_residual")
+    _count(1)
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float) -> None:
@@ -64,6 +84,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
     dim = x.shape[-1]
     check(library().pe_rmsnorm(dtype_tag(x.dtype), _ptr(x), _ptr(weight), _ptr(out), x.numel() // dim, dim, float(eps),
                                _stream()), "rmsnorm")
+    _count(1)
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -71,12 +92,14 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     n, two_i = gate_up.shape
     _need(two_i == 2 * out.shape[1] and out.shape[0] == n and out.dtype == gate_up.dtype, "silu_mul: shapes")
     check(library().pe_silu_mul(dtype_tag(gate_up.dtype), _ptr(gate_up), _ptr(out), n, out.shape[1], _stream()), "silu_mul")
+    _count(1)
 
 
 def batch_expand(seq_qstart: torch.Tensor, seq_past: torch.Tensor, n_seqs: int, token_seq: torch.Tensor,
                  token_pos: torch.Tensor) -> None:
     check(library().pe_batch_expand(_ptr(seq_qstart), _ptr(seq_past), n_seqs, _ptr(token_seq), _ptr(token_pos),
                                     _stream()), "batch_expand")
+    _count(1)
 
 
 def qk_norm_rope_append(qkv: torch.Tensor, n_tokens: int, n_heads: int, n_kv_heads: int, head_dim: int,
@@ -93,6 +116,7 @@ def qk_norm_rope_append(qkv: torch.Tensor, n_tokens: int, n_heads: int, n_kv_hea
         table_rows, _ptr(token_seq), _ptr(token_pos), _ptr(seq_slot), _ptr(page_table),
         0 if page_table is None else page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages),
         1 if write_cache else 0, _ptr(status), _stream()), "qk_norm_rope_append")
+    _count(1)
 
 
 def attention_generic_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, max_splits: int) -> int:
@@ -111,6 +135,7 @@ def attention_generic(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: 
         n_heads, n_kv_heads, head_dim, float(scale), int(window), _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot),
         _ptr(page_table), page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages), _ptr(scratch), split_keys,
         max_splits, _ptr(status), _stream()), "attention_generic")
+    _count(2 if decode else 1)
 
 
 def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float, seed: int,
@@ -120,9 +145,11 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, m
     check(library().pe_sample(_ptr(logits), logits.stride(0), n, vocab, float(temperature), int(top_k), float(top_p),
                               float(min_p), int(seed) & ((1 << 64) - 1), _ptr(row_request), _ptr(row_step),
                               _ptr(out_tokens), _stream()), "sample")
+    _count(1)
 
 
 def repetition_penalty(logits: torch.Tensor, recent: torch.Tensor, recent_count: torch.Tensor, penalty: float) -> None:
     n, vocab = logits.shape
     check(library().pe_repetition_penalty(_ptr(logits), logits.stride(0), n, vocab, _ptr(recent), recent.shape[1],
                                           _ptr(recent_count), float(penalty), _stream()), "repetition_penalty")
+    _count(1)

@@ -1,0 +1,335 @@
+"""Each CUDA kernel alone against its plain reference, at sizes other than the engine's."""
+import math
+import random
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+KTOL = {torch.float32: 2e-6, torch.bfloat16: 8e-3}   # one rounding of the output (2^-9 = 2e-3, a few ulps)
+
+
+@pytest.fixture(scope="module")
+def ops(pe):
+    pe.kernels.library()
+    return pe.kernels.ops
+
+
+def _status():
+    return torch.zeros(4, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_gather(ops, dtype):
+    torch.manual_seed(0)
+    table = torch.randn(515, 80, device=DEV).to(dtype)
+    ids = torch.tensor([0, 514, 7, 7, 300], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 80, device=DEV)
+    st = _status()
+    ops.embed_gather(table, ids, out, st)
+    assert torch.equal(out, table.float()[ids.long()])
+    assert st.tolist()[0] == 0
+    bad = torch.tensor([3, 515], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, 80, device=DEV)
+    ops.embed_gather(table, bad, out2, st)
+    assert st.tolist()[:3] == [1, 1, 515] and float(out2[1].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dim", [80, 1000, 4096, 5120])
+def test_rmsnorm_with_residual(ops, dtype, dim):
+    torch.manual_seed(1)
+    n = 7
+    res = torch.randn(n, dim, device=DEV) * 3
+    delta = torch.randn(n, dim, device=DEV).to(dtype)
+    w = 1 + 0.1 * torch.randn(dim, device=DEV)
+    eps = 3e-6
+    want_h = res + delta.float()
+    want = plain.rms_norm(want_h.cpu(), w.cpu(), eps)
+    # add + write back + norm
+    r1, out = res.clone(), torch.empty(n, dim, device=DEV, dtype=dtype)
+    ops.rmsnorm_residual(r1, delta, w, out, eps)
+    assert torch.equal(r1, want_h)
+    assert rel_err(out.float().cpu(), want) < KTOL[dtype]
+    # no delta: the stream is left alone
+    r2, out2 = res.clone(), torch.empty(n, dim, device=DEV, dtype=dtype)
+    ops.rmsnorm_residual(r2, None, w, out2, eps)
+    assert torch.equal(r2, res)
+    assert rel_err(out2.float().cpu(), plain.rms_norm(res.cpu(), w.cpu(), eps)) < KTOL[dtype]
+    # gathered rows: nothing written back
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=DEV)
+    r3, out3 = res.clone(), torch.empty(3, dim, device=DEV, dtype=dtype)
+    ops.rmsnorm_residual(r3, delta, w, out3, eps, rows)
+    assert torch.equal(r3, res)
+    assert rel_err(out3.float().cpu(), want[[5, 0, 5]]) < KTOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_plain(ops, dtype):
+    torch.manual_seed(2)
+    x = torch.randn(6, 5, 48, device=DEV).to(dtype)
+    w = 1 + 0.1 * torch.randn(48, device=DEV)
+    out = torch.empty_like(x)
+    ops.rmsnorm(x, w, out, 1e-5)
+    assert rel_err(out.float().cpu(), plain.rms_norm(x.float().cpu(), w.cpu(), 1e-5)) < KTOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,inter", [(1, 176), (9, 200), (33, 3072)])
+def test_silu_mul(ops, dtype, n, inter):
+    torch.manual_seed(3)
+    gu = (torch.randn(n, 2 * inter, device=DEV) * 4).to(dtype)
+    out = torch.empty(n, inter, device=DEV, dtype=dtype)
+    ops.silu_mul(gu, out)
+    g, u = gu.float().cpu()[:, :inter], gu.float().cpu()[:, inter:]
+    want = g / (1 + torch.exp(-g)) * u
+    assert rel_err(out.float().cpu(), want) < KTOL[dtype]
+
+
+class PagedSetup:
+    """A batch of sequences with keys and values scattered over shuffled pages of a pool."""
+
+    def __init__(self, lens, nkv, d, dtype, seed=0, extra_pages=5, key_scale=1.0):
+        g = torch.Generator().manual_seed(seed)
+        self.lens, self.nkv, self.d, self.dtype = lens, nkv, d, dtype
+        B = len(lens)
+        pages_per = [(L + 63) // 64 for L in lens]
+        self.num_pages = sum(pages_per) + extra_pages
+        order = list(range(self.num_pages))
+        random.Random(seed).shuffle(order)
+        self.table_width = max(pages_per) + 2
+        self.slots = list(range(B - 1, -1, -1))   # slot numbers differ from batch order
+        table = torch.full((B + 1, self.table_width), -1, dtype=torch.int32)
+        self.k = [(torch.randn(L, nkv, d, generator=g) * key_scale).to(dtype) for L in lens]
+        self.v = [torch.randn(L, nkv, d, generator=g).to(dtype) for L in lens]
+        kp = torch.randn(self.num_pages, nkv, 64, d, generator=g).to(dtype)   # junk where nothing was written
+        vp = torch.randn(self.num_pages, nkv, 64, d, generator=g).to(dtype)
+        it = iter(order)
+        for b, L in enumerate(lens):
+            for lp in range(pages_per[b]):
+                page = next(it)
+                table[self.slots[b], lp] = page
+                n = min(64, L - lp * 64)
+                kp[page, :, :n] = self.k[b][lp * 64: lp * 64 + n].transpose(0, 1)
+                vp[page, :, :n] = self.v[b][lp * 64: lp * 64 + n].transpose(0, 1)
+        self.k_pages, self.v_pages, self.table = kp.to(DEV), vp.to(DEV), table.to(DEV)
+        self.seq_slot = torch.tensor(self.slots, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d,rot", [(4, 2, 16, 16), (6, 2, 32, 32), (5, 5, 48, 48), (8, 1, 128, 64), (3, 3, 80, 80)])
+def test_qk_norm_rope_append(ops, dtype, nh, nkv, d, rot):
+    torch.manual_seed(4)
+    lens = [70, 3, 129]                 # lengths after the step
+    q_lens = [6, 3, 65]                 # tokens this step brings (the second sequence starts here)
+    ps = PagedSetup(lens, nkv, d, dtype, seed=4)
+    N = sum(q_lens)
+    ld = (nh + 2 * nkv) * d + 16        # row stride larger than the row
+    qkv = torch.randn(N, ld, device=DEV).to(dtype)
+    before = qkv.clone()
+    qw = 1 + 0.2 * torch.randn(d, device=DEV)
+    kw = 1 + 0.2 * torch.randn(d, device=DEV)
+    eps, theta, max_pos = 1e-5, 1e4, 256
+    inv = plain.rope_inv_freq(rot, theta)
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float32), inv)
+    cos, sin = torch.cos(ang).to(DEV), torch.sin(ang).to(DEV)
+    token_seq = torch.tensor(sum(([b] * n for b, n in enumerate(q_lens)), []), dtype=torch.int32, device=DEV)
+    pos_list = sum(([lens[b] - q_lens[b] + i for i in range(q_lens[b])] for b in range(3)), [])
+    token_pos = torch.tensor(pos_list, dtype=torch.int32, device=DEV)
+    k_before, v_before = ps.k_pages.clone(), ps.v_pages.clone()
+    st = _status()
+    ops.qk_norm_rope_append(qkv[:, : ld], N, nh, nkv, d, qw, kw, eps, cos, sin, rot, token_seq, token_pos, ps.seq_slot,
+                            ps.table, ps.num_pages, ps.k_pages, ps.v_pages, True, st)
+    assert st.tolist()[0] == 0
+    x = before.float().cpu()
+    q_in = x[:, : nh * d].view(N, nh, d)
+    k_in = x[:, nh * d: (nh + nkv) * d].view(N, nkv, d)
+    v_in = x[:, (nh + nkv) * d: (nh + 2 * nkv) * d].view(N, nkv, d)
+    c, s = plain.rope_cos_sin(torch.tensor(pos_list), rot, theta)
+    q_want = plain.rope_rotate_neox(plain.rms_norm(q_in, qw.cpu(), eps), c, s, rot)
+    k_want = plain.rope_rotate_neox(plain.rms_norm(k_in, kw.cpu(), eps), c, s, rot)
+    got = qkv.float().cpu()
+    assert rel_err(got[:, : nh * d].view(N, nh, d), q_want) < KTOL[dtype]
+    assert rel_err(got[:, nh * d: (nh + nkv) * d].view(N, nkv, d), k_want) < KTOL[dtype]
+    assert torch.equal(got[:, (nh + nkv) * d:], x[:, (nh + nkv) * d:])     # v and the padding are untouched
+    # the cache holds exactly the new rows, at their pages; every other row is as before
+    touched = torch.zeros(ps.num_pages, 64, dtype=torch.bool)
+    kp, vp = ps.k_pages.float().cpu(), ps.v_pages.float().cpu()
+    for t, (b, p) in enumerate(zip(token_seq.tolist(), pos_list)):
+        page = int(ps.table[ps.slots[b], p // 64])
+        touched[page, p % 64] = True
+        assert rel_err(kp[page, :, p % 64], k_want[t]) < KTOL[dtype]
+        assert torch.equal(vp[page, :, p % 64], v_in[t])
+    keep = ~touched
+    assert torch.equal(ps.k_pages.cpu().transpose(1, 2)[keep], k_before.cpu().transpose(1, 2)[keep])
+    assert torch.equal(ps.v_pages.cpu().transpose(1, 2)[keep], v_before.cpu().transpose(1, 2)[keep])
+    # write_cache off: q and k are still rewritten, the cache is not
+    k_now = ps.k_pages.clone()
+    qkv2 = before.clone()
+    ops.qk_norm_rope_append(qkv2, N, nh, nkv, d, qw, kw, eps, cos, sin, rot, token_seq, token_pos, ps.seq_slot,
+                            ps.table, ps.num_pages, ps.k_pages, ps.v_pages, False, st)
+    assert torch.equal(qkv2, qkv) and torch.equal(ps.k_pages, k_now)
+
+
+def _plain_attention(ps, q_list, pasts, nh, scale, window):
+    outs = []
+    for b, q in enumerate(q_list):
+        T = pasts[b] + q.shape[0]
+        outs.append(plain.causal_gqa_attention(q.float(), ps.k[b][:T].float(), ps.v[b][:T].float(), scale,
+                                               window=window, q_start=pasts[b]))
+    return torch.cat(outs, 0)
+
+
+ATT_TOL = {torch.float32: 5e-6, torch.bfloat16: 8e-3}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d", [(4, 2, 16), (6, 2, 32), (5, 5, 48), (8, 1, 128), (4, 1, 256), (2, 2, 80)])
+@pytest.mark.parametrize("window", [0, 37])
+def test_attention_prefill(ops, dtype, nh, nkv, d, window):
+    torch.manual_seed(5)
+    lens = [200, 1, 77, 64]
+    pasts = [0, 0, 50, 0]                # the third sequence continues an earlier chunk
+    q_lens = [L - p for L, p in zip(lens, pasts)]
+    ps = PagedSetup(lens, nkv, d, dtype, seed=5, key_scale=2.0)
+    N = sum(q_lens)
+    ld = nh * d + 32
+    q_all = torch.randn(N, ld, device=DEV).to(dtype)
+    out = torch.zeros(N, nh * d, device=DEV, dtype=dtype)
+    qstart = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    past_t = torch.tensor(pasts, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    st = _status()
+    ops.attention_generic(False, q_all, out, len(lens), max(q_lens), nh, nkv, d, scale, window, qstart, past_t,
+                          ps.seq_slot, ps.table, ps.num_pages, ps.k_pages, ps.v_pages, None, 0, 0, st)
+    assert st.tolist()[0] == 0
+    qs, o = [], 0
+    for n in q_lens:
+        qs.append(q_all[o:o + n, : nh * d].cpu().view(n, nh, d)); o += n
+    want = _plain_attention(ps, qs, pasts, nh, scale, window or None)
+    assert rel_err(out.float().cpu().view(N, nh, d), want) < ATT_TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,d", [(4, 2, 16), (6, 2, 32), (5, 5, 48), (32, 8, 128), (4, 1, 256), (16, 2, 64)])
+@pytest.mark.parametrize("window", [0, 300])
+def test_attention_decode(ops, dtype, nh, nkv, d, window):
+    torch.manual_seed(6)
+    lens = [1, 700, 256, 257, 33]        # one token, several ranges, a range's edge on both sides
+    pasts = [L - 1 for L in lens]
+    ps = PagedSetup(lens, nkv, d, dtype, seed=6, key_scale=2.0)
+    B = len(lens)
+    q_all = torch.randn(B, nh * d, device=DEV).to(dtype)
+    out = torch.zeros(B, nh * d, device=DEV, dtype=dtype)
+    qstart = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    past_t = torch.tensor(pasts, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    split_keys, max_splits = 256, 4       # 4 ranges allowed although the longest needs 3
+    scratch = torch.full((ops.attention_generic_scratch_floats(B, nh, d, max_splits),), float("nan"), device=DEV)
+    st = _status()
+    ops.attention_generic(True, q_all, out, B, 1, nh, nkv, d, scale, window, qstart, past_t, ps.seq_slot, ps.table,
+                          ps.num_pages, ps.k_pages, ps.v_pages, scratch, split_keys, max_splits, st)
+    assert st.tolist()[0] == 0
+    qs = [q_all[b: b + 1].cpu().view(1, nh, d) for b in range(B)]
+    want = _plain_attention(ps, qs, pasts, nh, scale, window or None)
+    assert rel_err(out.float().cpu().view(B, nh, d), want) < ATT_TOL[dtype]
+
+
+@pytest.mark.parametrize("decode", [False, True])
+def test_attention_finds_a_far_key(ops, decode):
+    """One key among hundreds matches the query; the output must be that key's value."""
+    nh, nkv, d = 4, 2, 32
+    L, far = 650, 13
+    ps = PagedSetup([L], nkv, d, torch.float32, seed=7, key_scale=0.05)
+    q = torch.zeros(1, nh * d)
+    probe = torch.randn(d)
+    probe = probe / probe.norm() * 12.0
+    for h in range(nh):
+        q[0, h * d:(h + 1) * d] = probe
+    page = int(ps.table[ps.slots[0], far // 64])
+    ps.k_pages[page, :, far % 64] = probe.to(DEV) * 2.0       # score 288*scale against ~0 elsewhere
+    q_lens = [1]
+    out = torch.zeros(1, nh * d, device=DEV)
+    qstart = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    past_t = torch.tensor([L - 1], dtype=torch.int32, device=DEV)
+    scratch = torch.zeros(ops.attention_generic_scratch_floats(1, nh, d, 3), device=DEV)
+    ops.attention_generic(decode, q.to(DEV), out, 1, 1, nh, nkv, d, 1 / math.sqrt(d), 0, qstart, past_t, ps.seq_slot,
+                          ps.table, ps.num_pages, ps.k_pages, ps.v_pages, scratch if decode else None,
+                          256 if decode else 0, 3 if decode else 0, _status())
+    v_far = ps.v_pages[page, :, far % 64].cpu()               # [nkv, d]
+    got = out.cpu().view(nh, d)
+    for h in range(nh):
+        assert torch.allclose(got[h], v_far[h // 2], atol=1e-4)
+
+
+def test_sampler_greedy_and_ties(ops):
+    torch.manual_seed(8)
+    logits = torch.randn(6, 1000, device=DEV)
+    logits[2, 17] = logits[2, 900] = 50.0                     # a tie: the lower index wins
+    logits[3, 999] = 60.0
+    req = torch.arange(6, dtype=torch.int32, device=DEV)
+    step = torch.zeros(6, dtype=torch.int32, device=DEV)
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops.sample(logits, 0.0, 0, 1.0, 0.0, 1, req, step, out)
+    want = logits.argmax(-1).tolist()
+    want[2] = 17
+    assert out.tolist() == want
+
+
+@pytest.mark.parametrize("filters", [dict(), dict(top_k=5), dict(top_k=40, top_p=0.9, min_p=0.05), dict(top_p=0.6),
+                                     dict(min_p=0.2), dict(top_k=1500)])
+def test_sampler_matches_the_plain_draw(ops, filters):
+    torch.manual_seed(9)
+    V, rows = 2000, 24
+    logits = torch.randn(rows, V, device=DEV) * 2.5
+    req = torch.arange(rows, dtype=torch.int32, device=DEV) % 5
+    step = torch.arange(rows, dtype=torch.int32, device=DEV) // 5
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    kw = dict(top_k=0, top_p=1.0, min_p=0.0)
+    kw.update(filters)
+    ops.sample(logits, 0.8, kw["top_k"], kw["top_p"], kw["min_p"], 1234, req, step, out)
+    got = out.tolist()
+    agree = 0
+    for r in range(rows):
+        want = plain.sample_token(logits[r].cpu(), seed=1234, request=int(req[r]), step=int(step[r]), temperature=0.8, **kw)
+        _, probs = plain.filter_logits(logits[r].cpu(), temperature=0.8, **kw)
+        assert probs[got[r]] > 0, "the kernel drew a token that the filters exclude"
+        agree += got[r] == want
+    assert agree >= rows - 1     # float32 vs float64 Gumbel arithmetic may flip one near-tie
+
+
+def test_sampler_is_keyed_by_request_and_step_not_by_row(ops):
+    torch.manual_seed(10)
+    row = torch.randn(1, 3000, device=DEV)
+    logits = row.repeat(4, 1)
+    req = torch.tensor([3, 3, 4, 3], dtype=torch.int32, device=DEV)
+    step = torch.tensor([0, 1, 0, 0], dtype=torch.int32, device=DEV)
+    out = torch.empty(4, dtype=torch.int32, device=DEV)
+    ops.sample(logits, 1.0, 0, 1.0, 0.0, 77, req, step, out)
+    a = out.tolist()
+    assert a[0] == a[3] and len({a[0], a[1], a[2]}) >= 2
+    ops.sample(logits, 1.0, 0, 1.0, 0.0, 78, req, step, out)
+    assert out.tolist() != a
+
+
+def test_repetition_penalty(ops):
+    logits = torch.tensor([[2.0, -1.0, 0.5, 3.0], [1.0, 1.0, 1.0, 1.0]], device=DEV)
+    recent = torch.tensor([[3, 1, 3, 0], [2, 0, 0, 0]], dtype=torch.int32, device=DEV)
+    count = torch.tensor([3, 1], dtype=torch.int32, device=DEV)
+    ops.repetition_penalty(logits, recent, count, 2.0)
+    assert logits.tolist() == [[2.0, -2.0, 0.5, 1.5], [1.0, 1.0, 0.5, 1.0]]
+
+
+def test_unsupported_sizes_are_refused(pe, ops):
+    q = torch.zeros(1, 1024, device=DEV)
+    with pytest.raises(pe.kernels.KernelError, match="size"):
+        ops.attention_generic(False, q, q.clone(), 1, 1, 1, 1, 1024, 1.0, 0, torch.zeros(2, dtype=torch.int32, device=DEV),
+                              torch.zeros(1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                              torch.zeros(1, 1, dtype=torch.int32, device=DEV), 1, q, q, None, 0, 0, _status())
+    with pytest.raises(pe.kernels.KernelError):
+        ops.embed_gather(torch.zeros(4, 4), torch.zeros(1, dtype=torch.int32), torch.zeros(1, 4), torch.zeros(4, dtype=torch.int32))

@@ -1,0 +1,292 @@
+"""The engine against the plain implementation, in float32 and bfloat16: whole requests, the last
+tokens one by one, unequal batches with slots used again, long decoding, the first tokens,
+generation through the entry point, and the replay program itself."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from conftest import ROOT, TEST_CONFIGS, TOL, rel_err
+
+pytestmark = pytest.mark.gpu
+KEYS = ["A", "B", "C"]
+DTYPES = ["float32", "bfloat16"]
+
+
+def _tokens(vocab, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+@pytest.fixture(scope="module")
+def oracles(model_folders):
+    return {k: plain.load_folder(f) for k, f in model_folders.items()}
+
+
+@pytest.fixture(scope="module")
+def engines(pe, model_folders):
+    made = {}
+
+    def get(key, dtype, **kw):
+        ident = (key, dtype, tuple(sorted(kw.items())))
+        if ident not in made:
+            args = dict(dtype=dtype, max_cache_tokens=64 * 40, max_batch=8)
+            args.update(kw)
+            made[ident] = pe.Engine(model_folders[key], **args)
+        return made[ident]
+
+    return get
+
+
+class Replay:
+    """Drives the engine's replayer in-process and collects logits per (request, position)."""
+
+    def __init__(self, pe, engine, tmp_path):
+        self.rep = pe.engine.replay.TraceReplayer(engine, str(tmp_path))
+        self.step = 0
+        self.fed = {}
+        self.got = {}
+
+    def run(self, entries, end=()):
+        rec = {"step": self.step, "entries": [{"id": i, "tokens": t, "want": w} for i, t, w in entries], "end": list(end)}
+        path = self.rep.run_step(rec)
+        vocab = self.rep.engine.config.vocab_size
+        n_want = sum(len(w) for _, _, w in entries)
+        if n_want:
+            arr = torch.frombuffer(bytearray(open(path, "rb").read()), dtype=torch.float32).view(n_want, vocab)
+            r = 0
+            for i, t, w in entries:
+                base = self.fed.get(i, 0)
+                for j in w:
+                    self.got[(i, base + j)] = arr[r].clone()
+                    r += 1
+        else:
+            assert path is None
+        for i, t, _ in entries:
+            self.fed[i] = self.fed.get(i, 0) + len(t)
+        for i in end:
+            self.fed.pop(i, None)
+        self.step += 1
+
+
+def _check(got, oracle_rows, dtype, what):
+    worst = 0.0
+    scale = max(float(r.abs().max()) for r in oracle_rows.values())
+    for key, ref in oracle_rows.items():
+        err = float((got[key].double() - ref.double()).abs().max()) / scale
+        worst = max(worst, err)
+    assert worst < TOL[dtype], f"{what}: worst error {worst:.3e} (limit {TOL[dtype]:.0e})"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("key", KEYS)
+def test_each_request_alone_and_whole(pe, engines, oracles, tmp_path, key, dtype):
+    cfg, w = oracles[key]
+    eng = engines(key, dtype)
+    for n, seed in [(150, 1), (1, 2), (65, 3), (333, 4)]:
+        toks = _tokens(cfg["vocab_size"], n, seed)
+        rp = Replay(pe, eng, tmp_path)
+        rp.run([("r", toks, list(range(n)))], end=["r"])
+        ref = plain.forward_logits(cfg, w, toks)
+        _check(rp.got, {("r", i): ref[i] for i in range(n)}, dtype, f"{key} whole, {n} tokens")
+    assert not eng.cache.live_slots
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("key", KEYS)
+def test_last_32_tokens_one_by_one(pe, engines, oracles, tmp_path, key, dtype):
+    cfg, w = oracles[key]
+    eng = engines(key, dtype)
+    for n, seed in [(33, 5), (100, 6), (290, 7)]:
+        toks = _tokens(cfg["vocab_size"], n, seed)
+        rp = Replay(pe, eng, tmp_path)
+        head = n - 32
+        rp.run([("r", toks[:head], [head - 1])])
+        for i in range(head, n):
+            rp.run([("r", [toks[i]], [0])], end=["r"] if i == n - 1 else [])
+        ref = plain.forward_logits(cfg, w, toks)
+        _check(rp.got, {("r", i): ref[i] for i in range(head - 1, n)}, dtype, f"{key} last 32 of {n}")
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("key", KEYS)
+def test_unequal_batches_one_after_another(pe, engines, oracles, tmp_path, key, dtype):
+    """Two batches; in each, prompts of unequal lengths go in together, every request is then fed
+    its remaining tokens one per step, and the shorter requests end earlier.  The second batch gets
+    the slots and pages that the first gave back."""
+    cfg, w = oracles[key]
+    eng = engines(key, dtype)
+    rp = Replay(pe, eng, tmp_path)
+    want = {}
+    plans = [
+        [("a", 5, 9), ("b", 70, 3), ("c", 130, 40), ("d", 1, 20)],      # (id, prompt length, decoded tokens)
+        [("e", 64, 12), ("f", 9, 30), ("g", 200, 1), ("h", 33, 33), ("i", 2, 5)],
+    ]
+    seed = 10
+    slots_seen = []
+    for plan in plans:
+        seqs = {}
+        for rid, p, dec in plan:
+            seed += 1
+            seqs[rid] = _tokens(cfg["vocab_size"], p + dec, seed)
+        rp.run([(rid, seqs[rid][:p], [p - 1]) for rid, p, dec in plan])
+        slots_seen.append(sorted(rp.rep.slots.values()))
+        for k in range(max(dec for _, _, dec in plan)):
+            live = [(rid, p, dec) for rid, p, dec in plan if k < dec]
+            rp.run([(rid, [seqs[rid][p + k]], [0]) for rid, p, dec in live],
+                   end=[rid for rid, p, dec in live if k == dec - 1])
+        for rid, p, dec in plan:
+            ref = plain.forward_logits(cfg, w, seqs[rid])
+            for i in range(p - 1, p + dec):
+                want[(rid, i)] = ref[i]
+        assert not eng.cache.live_slots
+        eng.cache.check()
+    assert set(slots_seen[0]) <= set(slots_seen[1])      # the second batch used the first one's slots again
+    _check(rp.got, want, dtype, f"{key} unequal batches")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("key", ["A", "B"])
+def test_long_decoding_and_first_tokens(pe, engines, oracles, tmp_path, key, dtype):
+    cfg, w = oracles[key]
+    eng = engines(key, dtype)
+    n = 600
+    toks = _tokens(cfg["vocab_size"], n, 30)
+    rp = Replay(pe, eng, tmp_path)
+    rp.run([("r", toks[:1], [0])])                         # a sequence's very first token, alone
+    for i in range(1, n):
+        rp.run([("r", [toks[i]], [0])], end=["r"] if i == n - 1 else [])
+    ref = plain.forward_logits(cfg, w, toks)
+    _check(rp.got, {("r", i): ref[i] for i in range(n)}, dtype, f"{key} {n} tokens one by one")
+    _check({k: v for k, v in rp.got.items() if k[1] < 3}, {("r", i): ref[i] for i in range(3)}, dtype, "first tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_graph_replay_equals_eager_steps(pe, engines, oracles, tmp_path, dtype):
+    cfg, w = oracles["B"]
+    toks = [_tokens(cfg["vocab_size"], 90, 40 + i) for i in range(3)]
+    outs = []
+    for graphs in (True, False):
+        eng = engines("B", dtype, enable_cuda_graph=graphs)
+        rp = Replay(pe, eng, tmp_path)
+        rp.run([(str(i), t[:50 + i], [49 + i]) for i, t in enumerate(toks)])
+        for k in range(30):
+            rp.run([(str(i), [t[50 + i + k]], [0]) for i, t in enumerate(toks)], end=[str(i) for i in range(3)] if k == 29 else [])
+        outs.append(rp.got)
+        assert bool(eng.runner._graphs) == graphs
+    for k in outs[0]:
+        assert torch.equal(outs[0][k], outs[1][k]), f"graph and eager steps differ at {k}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("key", KEYS)
+def test_greedy_generation_through_the_entry_point(pe, engines, oracles, key, dtype):
+    cfg, w = oracles[key]
+    eng = engines(key, dtype)
+    prompts = [_tokens(cfg["vocab_size"], n, 50 + n) for n in (5, 9, 13, 70)]
+    params = pe.SamplingParams(max_tokens=8, temperature=0.0, top_k=0, top_p=1.0, min_p=0.0)
+    results = eng.generate(prompts, params)
+    assert not eng.cache.live_slots
+    for p, r in zip(prompts, results):
+        assert r.prompt_tokens == len(p) and r.finish_reason in ("length", "stop")
+        if r.finish_reason == "length":
+            assert r.completion_tokens == 8
+        # every chosen token is the plain implementation's argmax, or within rounding of it
+        ref = plain.forward_logits(cfg, w, p + r.token_ids)
+        scale = float(ref.abs().max())
+        for j, tok in enumerate(r.token_ids):
+            row = ref[len(p) - 1 + j]
+            assert float(row.max() - row[tok]) <= 2 * TOL[dtype] * scale, f"token {j} of a {len(p)}-token prompt"
+    if dtype == "float32":
+        for p, r in zip(prompts[:2], results[:2]):
+            stops = cfg.get("eos_token_id", [])
+            stops = stops if isinstance(stops, list) else [stops]
+            assert r.token_ids == plain.generate_greedy(cfg, w, p, 8, stop_ids=stops)
+    single = eng.generate(prompts[1], params)
+    assert single.token_ids == results[1].token_ids
+
+
+def test_stop_token_and_context_limit(pe, engines, oracles):
+    cfg, w = oracles["A"]
+    eng = engines("A", "float32")
+    prompt = _tokens(cfg["vocab_size"], 6, 60)
+    free = eng.generate(prompt, pe.SamplingParams.greedy_params(max_tokens=6))
+    assert free.completion_tokens == 6
+    stopped = eng.generate(prompt, pe.SamplingParams.greedy_params(max_tokens=6, stop_token_ids=[free.token_ids[3]]))
+    first = free.token_ids.index(free.token_ids[3])
+    assert stopped.token_ids == free.token_ids[:first] and stopped.finish_reason == "stop"
+    small = engines("A", "float32", max_context_len=16, max_cache_tokens=64)
+    r = small.generate(_tokens(cfg["vocab_size"], 12, 61), pe.SamplingParams.greedy_params(max_tokens=50))
+    assert r.completion_tokens == 4 and r.finish_reason == "length"
+    with pytest.raises(ValueError, match="context"):
+        small.generate(_tokens(cfg["vocab_size"], 17, 62), pe.SamplingParams.greedy_params(max_tokens=1))
+
+
+def test_seeded_sampling_does_not_depend_on_batching(pe, engines, oracles):
+    cfg, w = oracles["B"]
+    prompts = [_tokens(cfg["vocab_size"], n, 70 + n) for n in (1, 7, 31, 64)]
+    params = pe.SamplingParams(max_tokens=16, temperature=0.8, seed=11)
+    together = engines("B", "float32").generate(prompts, params)
+    again = engines("B", "float32").generate(prompts, params)
+    assert [r.token_ids for r in together] == [r.token_ids for r in again]
+    one_by_one = engines("B", "float32", max_batch=1).generate(prompts, params)
+    assert [r.token_ids for r in together] == [r.token_ids for r in one_by_one]
+    other = engines("B", "float32").generate(prompts, pe.SamplingParams(max_tokens=16, temperature=0.8, seed=12))
+    assert [r.token_ids for r in together] != [r.token_ids for r in other]
+    # the draws follow the plain restatement of the filters and the generator
+    r0 = together[0]
+    ref = plain.forward_logits(cfg, w, prompts[0] + r0.token_ids)
+    for j, tok in enumerate(r0.token_ids[:6]):
+        _, probs = plain.filter_logits(ref[len(prompts[0]) - 1 + j], temperature=0.8, top_k=40, top_p=0.95, min_p=0.05)
+        assert probs[tok] > 0
+
+
+def test_cache_too_small_is_an_error_not_a_wrong_result(pe, engines, oracles):
+    cfg, w = oracles["A"]
+    eng = engines("A", "float32", max_cache_tokens=128, max_context_len=128)
+    s = eng.alloc_slot()
+    with pytest.raises(pe.cache.CacheFull):
+        eng.step([pe.StepEntry(s, _tokens(cfg["vocab_size"], 129, 80), (0,))])
+    assert eng.cache.length(s) == 0
+    eng.free_slot(s)
+    with pytest.raises(pe.kernels.KernelError, match="token id"):
+        s = eng.alloc_slot()
+        try:
+            eng.step([pe.StepEntry(s, [cfg["vocab_size"] + 3], (0,))])
+        finally:
+            eng.free_slot(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_run_program(pe, model_folders, oracles, tmp_path, dtype):
+    """The program itself, as a user runs it: steps on standard input, ``done`` lines, .f32 files."""
+    cfg, w = oracles["B"]
+    a, b = _tokens(cfg["vocab_size"], 75, 90), _tokens(cfg["vocab_size"], 20, 91)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:70], "want": [0, 69]}, {"id": "b", "tokens": b[:18], "want": [17]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": [a[70]], "want": [0]}, {"id": "b", "tokens": [b[18]], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": [a[71]], "want": [0]}, {"id": "b", "tokens": [b[19]], "want": [0]}], "end": ["b"]},
+             {"step": 3, "entries": [{"id": "a", "tokens": [a[72]], "want": []}], "end": []},
+             {"step": 7, "entries": [{"id": "a", "tokens": [a[73]], "want": [0]}, ], "end": ["a"]},
+             {"step": 8, "entries": [{"id": "c", "tokens": b, "want": [19]}], "end": ["c"]}]
+    out = tmp_path / "out"
+    env = dict(os.environ)
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_folders["B"], "--dtype", dtype,
+                           "--out", str(out), "--max-tokens", "192"],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, env=env, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == ["done", "0", "done", "1", "done", "2", "done", "3", "done", "7", "done", "8"]
+    assert sorted(os.listdir(out)) == ["0.f32", "1.f32", "2.f32", "7.f32", "8.f32"]
+    V = cfg["vocab_size"]
+    read = lambda s: torch.frombuffer(bytearray(open(out / f"{s}.f32", "rb").read()), dtype=torch.float32).view(-1, V)
+    ra, rb = plain.forward_logits(cfg, w, a), plain.forward_logits(cfg, w, b)
+    got = {("a", 0): read(0)[0], ("a", 69): read(0)[1], ("b", 17): read(0)[2], ("a", 70): read(1)[0],
+           ("a", 71): read(2)[0], ("b", 19): read(2)[1], ("a", 73): read(7)[0], ("c", 19): read(8)[0]}
+    assert read(0).shape == (3, V) and read(1).shape == (1, V)
+    want = {k: (ra if k[0] == "a" else rb)[k[1]] for k in got}
+    _check(got, want, dtype, "trace_run")

@@ -1,0 +1,311 @@
+"""Each part alone against its plain formula, and a toy architecture whose mixer keeps state of its
+own: registered, built and stepped from the test, with no change to the package's files."""
+import math
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+PTOL = {torch.float32: 1e-5, torch.bfloat16: 1.5e-2}
+
+
+def _ctx(pe, rt, cache, slots, tokens_per_seq, want=()):
+    """A step context for sequences that bring ``tokens_per_seq`` tokens each (all tokens zero)."""
+    entries = [pe.StepEntry(s, [0] * n, ()) for s, n in zip(slots, tokens_per_seq)]
+    pasts = [cache.length(s) for s in slots]
+    for s, p, n in zip(slots, pasts, tokens_per_seq):
+        cache.reserve(s, p + n)
+    ints, n_tokens, n_want = pe.engine.StepContext.pack_meta(entries, pasts)
+    pool = pe.engine.BufferPool(DEV)
+    ctx = pe.engine.StepContext(rt, pool, n_tokens=n_tokens, n_seqs=len(slots), max_q=max(tokens_per_seq),
+                                decode=all(n == 1 for n in tokens_per_seq),
+                                max_kv_len=max(p + n for p, n in zip(pasts, tokens_per_seq)), n_want=0)
+    ctx.meta.copy_(torch.tensor(ints, dtype=torch.int32))
+    pe.kernels.ops.batch_expand(ctx.seq_qstart, ctx.seq_past, len(slots), ctx.token_seq, ctx.token_pos)
+    return ctx, pasts
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_part(pe, dtype):
+    rt = pe.parts.Runtime(DEV, dtype)
+    w = (1 + 0.1 * torch.randn(200)).to(torch.bfloat16)
+    norm = pe.parts.lookup("norm", "rmsnorm")({"dim": 200, "eps": 2e-5}, {"weight": w}, rt)
+    assert norm.weight.dtype == torch.float32
+    stream = torch.randn(9, 200, device=DEV)
+    delta = torch.randn(9, 200, device=DEV).to(dtype)
+    out = torch.empty(9, 200, device=DEV, dtype=dtype)
+    before = stream.clone()
+    norm.add_forward(stream, delta, out)
+    assert torch.equal(stream, before + delta.float())
+    assert rel_err(out.float().cpu(), plain.rms_norm(stream.cpu(), w.float(), 2e-5)) < PTOL[dtype]
+
+
+def test_rope_part_tables(pe):
+    rt = pe.parts.Runtime(DEV, torch.float32)
+    rope = pe.parts.lookup("position", "rope")({"rotary_dim": 48, "theta": 5e5, "max_positions": 700}, {}, rt)
+    cos, sin, rot = rope.tables()
+    c, s = plain.rope_cos_sin(torch.arange(700), 48, 5e5)
+    assert rot == 48 and cos.shape == (700, 24)
+    assert float((cos.cpu() - c).abs().max()) < 1e-6 and float((sin.cpu() - s).abs().max()) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [None, 50])
+def test_attention_part_prefill_then_decode(pe, dtype, window):
+    """The attention part alone over a small cache: two sequences, a prompt each, then single tokens."""
+    torch.manual_seed(0)
+    H, nh, nkv, d = 72, 6, 3, 24
+    rt = pe.parts.Runtime(DEV, dtype)
+    wts = {"q_proj": torch.randn(nh * d, H) * 0.2, "k_proj": torch.randn(nkv * d, H) * 0.2,
+           "v_proj": torch.randn(nkv * d, H) * 0.2, "o_proj": torch.randn(H, nh * d) * 0.2,
+           "q_norm": 3 + torch.randn(d) * 0.1, "k_norm": 1 + torch.randn(d) * 0.1}
+    wts = {k: v.to(torch.bfloat16) for k, v in wts.items()}
+    rope = pe.parts.lookup("position", "rope")({"rotary_dim": d, "theta": 1e4, "max_positions": 256}, {}, rt)
+    params = {"hidden": H, "n_heads": nh, "n_kv_heads": nkv, "head_dim": d, "qk_norm": True, "eps": 1e-6,
+              "scale": None, "window": window, "position": "rope"}
+    cls = pe.parts.lookup("mixer", "attention")
+    att = cls(params, wts, rt, positions={"rope": rope})
+    cache = pe.cache.PagedCache({0: cls.cache_request(params)}, max_tokens=512, max_slots=4, max_seq_len=256,
+                                dtype=dtype, device=DEV)
+    slots = [cache.alloc_slot(), cache.alloc_slot()]
+    lens = [90, 7]
+    xs = [torch.randn(L + 5, H).to(torch.bfloat16) for L in lens]       # inputs: prompt plus five more tokens
+    got = [[], []]
+    ctx, pasts = _ctx(pe, rt, cache, slots, lens)
+    x = torch.cat([xs[0][:90], xs[1][:7]]).to(DEV, dtype)
+    y = att.forward(x, ctx, cache.view(0)).float().cpu()
+    got[0].append(y[:90]); got[1].append(y[90:])
+    for s, L in zip(slots, lens):
+        cache.commit(s, L)
+    for k in range(5):
+        ctx, pasts = _ctx(pe, rt, cache, slots, [1, 1])
+        x = torch.stack([xs[0][90 + k], xs[1][7 + k]]).to(DEV, dtype)
+        y = att.forward(x, ctx, cache.view(0)).float().cpu()
+        got[0].append(y[0:1]); got[1].append(y[1:2])
+        for s in slots:
+            cache.commit(s, cache.length(s) + 1)
+    assert rt.status.tolist()[0] == 0
+    w = {f"p.self_attn.{k}.weight": v for k, v in wts.items()}
+    for b in range(2):
+        want = plain.attention_layer(xs[b].float(), w, "p", n_heads=nh, n_kv_heads=nkv, head_dim=d, eps=1e-6,
+                                     theta=1e4, window=window)
+        assert rel_err(torch.cat(got[b]), want) < PTOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_embedding_and_head_parts(pe, dtype):
+    torch.manual_seed(1)
+    rt = pe.parts.Runtime(DEV, dtype)
+    H, I, V = 80, 176, 515
+    wts = {"gate_proj": torch.randn(I, H) * 0.2, "up_proj": torch.randn(I, H) * 0.2, "down_proj": torch.randn(H, I) * 0.2}
+    wts = {k: v.to(torch.bfloat16) for k, v in wts.items()}
+    ffn = pe.parts.lookup("feed_forward", "swiglu")({"hidden": H, "intermediate": I}, wts, rt)
+    x = torch.randn(11, H).to(torch.bfloat16)
+
+    class Ctx:
+        pool = pe.engine.BufferPool(DEV)
+        def buffer(self, name, shape, dt):
+            return self.pool.get(name, shape, dt)
+
+    y = ffn.forward(x.to(DEV, dtype), Ctx()).float().cpu()
+    want = plain.swiglu(x.float(), wts["gate_proj"], wts["up_proj"], wts["down_proj"])
+    assert rel_err(y, want) < PTOL[dtype]
+    table = (torch.randn(V, H) * 0.5).to(torch.bfloat16)
+    emb = pe.parts.lookup("embedding", "token_embedding")({"vocab": V, "hidden": H}, {"weight": table}, rt)
+    head = pe.parts.lookup("head", "linear_head")({"vocab": V, "hidden": H}, {"weight": table}, rt)
+    assert head.weight.data_ptr() == emb.weight.data_ptr()        # a tied head shares the table
+    ids = torch.tensor([0, 514, 3], dtype=torch.int32, device=DEV)
+    out = torch.empty(3, H, device=DEV)
+    emb.forward(ids, out)
+    assert torch.equal(out.cpu(), table.float()[[0, 514, 3]])
+    logits = head.forward(x[:4].to(DEV, dtype))
+    assert logits.dtype == torch.float32
+    assert rel_err(logits.cpu(), x[:4].float() @ table.float().T) < PTOL[dtype]
+
+
+# ---- a toy architecture with a mixer that keeps fixed-size state -------------------------------------
+@dataclass(frozen=True)
+class ToyConfig:
+    hidden_size: int
+    vocab_size: int
+    layers: int
+    decay: float
+    max_position_embeddings: int = 256
+    architecture: str = "ToyRunningMeanLM"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["hidden_size"], d["vocab_size"], d["layers"], d["decay"])
+
+    def to_dict(self):
+        return {"architectures": [self.architecture], "hidden_size": self.hidden_size, "vocab_size": self.vocab_size,
+                "layers": self.layers, "decay": self.decay}
+
+    max_positions = property(lambda self: self.max_position_embeddings)
+    stop_token_ids = ()
+    bos_token = 0
+
+
+class DecayingSumMixer:
+    """state <- decay * state + W x_t ; output_t = state (per sequence, in token order).  The state
+    is fixed-size per sequence and lives in the cache's state group."""
+
+    @classmethod
+    def weight_decls(cls, params):
+        from importlib import import_module
+        WeightDecl = import_module("pytorch-engine_b200").parts.WeightDecl
+        return {"proj": WeightDecl((params["hidden"], params["hidden"]))}
+
+    @classmethod
+    def cache_request(cls, params):
+        from importlib import import_module
+        CR = import_module("pytorch-engine_b200").parts.CacheRequest
+        return CR("state", state_shapes=(("acc", (params["hidden"],), "float32"),))
+
+    def __init__(self, params, weights, runtime):
+        self.rt, self.decay = runtime, float(params["decay"])
+        self.proj = runtime.adopt(weights["proj"])
+
+    def forward(self, x, ctx, view):
+        z = self.rt.linear(x, self.proj).float()
+        state = view.state("acc")
+        out = torch.empty_like(z)
+        qs = ctx.seq_qstart.tolist()
+        for b, slot in enumerate(ctx.seq_slot.tolist()):
+            acc = state[slot]
+            for t in range(qs[b], qs[b + 1]):
+                acc = self.decay * acc + z[t]
+                out[t] = acc
+            state[slot] = acc
+        return out.to(x.dtype)
+
+
+def test_toy_mixer_with_state_of_its_own(pe):
+    P, B, R = pe.parts.PartSpec, pe.parts.BlockSpec, pe.parts.RunStep
+
+    def plan(cfg):
+        h = cfg.hidden_size
+        norm = lambda n: P("rmsnorm", {"dim": h, "eps": 1e-6}, {"weight": n})
+        blocks = tuple(B("pre_norm", norm(f"l{i}.n1"), P("decaying_sum", {"hidden": h, "decay": cfg.decay}, {"proj": f"l{i}.proj"}),
+                         norm(f"l{i}.n2"), P("swiglu", {"hidden": h, "intermediate": 2 * h},
+                                             {"gate_proj": f"l{i}.g", "up_proj": f"l{i}.u", "down_proj": f"l{i}.d"}),
+                         name=f"toy {i}") for i in range(cfg.layers))
+        return pe.parts.ModelPlan(hidden_size=h, vocab_size=cfg.vocab_size, max_positions=cfg.max_position_embeddings,
+                                  embedding=P("token_embedding", {"vocab": cfg.vocab_size, "hidden": h}, {"weight": "emb"}),
+                                  blocks=blocks, order=tuple(R(i) for i in range(cfg.layers)), final_norm=norm("fn"),
+                                  head=P("linear_head", {"vocab": cfg.vocab_size, "hidden": h}, {"weight": "emb"}))
+
+    pe.parts.register("mixer", "decaying_sum", DecayingSumMixer, replace=True)
+    pe.register_architecture("ToyRunningMeanLM", ToyConfig, plan, replace=True)
+    try:
+        cfg = ToyConfig(hidden_size=48, vocab_size=97, layers=2, decay=0.75)
+        eng = pe.Engine.from_random(cfg, seed=4, dtype="float32", max_cache_tokens=256, max_batch=4)
+        assert [g.request.kind for g in eng.cache.groups] == ["state"]
+        w = {k: v.float().cpu() for k, v in pe.weights.random_weights(eng.plan, 4, device=DEV).items()}
+
+        def plain_toy(tokens):
+            x = w["emb"][tokens]
+            for i in range(2):
+                n = plain.rms_norm(x, w[f"l{i}.n1"], 1e-6)
+                z = n @ w[f"l{i}.proj"].T
+                acc, rows = torch.zeros(48), []
+                for t in range(len(tokens)):
+                    acc = 0.75 * acc + z[t]
+                    rows.append(acc)
+                x = x + torch.stack(rows)
+                x = x + plain.swiglu(plain.rms_norm(x, w[f"l{i}.n2"], 1e-6), w[f"l{i}.g"], w[f"l{i}.u"], w[f"l{i}.d"])
+            return plain.rms_norm(x, w["fn"], 1e-6) @ w["emb"].T
+
+        seqs = [[5, 9, 2, 77, 31, 8, 8, 40], [96, 0, 3, 3, 14]]
+        for rnd in range(2):                                        # second round: the slots' state must start at zero
+            slots = [eng.alloc_slot(), eng.alloc_slot()]
+            got = [[], []]
+            lg = eng.step([pe.StepEntry(slots[0], seqs[0][:5], (0, 4)), pe.StepEntry(slots[1], seqs[1][:2], (1,))])
+            got[0] += [lg[0].cpu(), lg[1].cpu()]; got[1].append(lg[2].cpu())
+            for k in range(3):
+                lg = eng.step([pe.StepEntry(slots[0], [seqs[0][5 + k]], (0,)), pe.StepEntry(slots[1], [seqs[1][2 + k]], (0,))])
+                got[0].append(lg[0].cpu()); got[1].append(lg[1].cpu())
+            for s in slots:
+                eng.free_slot(s)
+            ref0, ref1 = plain_toy(seqs[0]), plain_toy(seqs[1])
+            assert rel_err(torch.stack(got[0]), ref0[[0, 4, 5, 6, 7]]) < 1e-5
+            assert rel_err(torch.stack(got[1]), ref1[[1, 2, 3, 4]]) < 1e-5
+        res = eng.generate([seqs[0][:3]], pe.SamplingParams.greedy_params(max_tokens=4))
+        assert res[0].completion_tokens == 4
+    finally:
+        pe.parts.unregister("mixer", "decaying_sum")
+        pe.config.unregister_architecture("ToyRunningMeanLM")
+
+
+def test_order_is_data_a_block_twice_and_a_shared_cache(pe):
+    """The plan's order may name a block twice (with a cache entry of its own for the second run) and
+    let a block read another block's keys and values without writing."""
+    from conftest import TEST_CONFIGS
+    cfg = pe.Qwen3Config.from_dict(dict(TEST_CONFIGS["A"], tie_word_embeddings=True))
+    base = pe.config.architecture("Qwen3ForCausalLM").plan(cfg)
+    R = pe.parts.RunStep
+    import dataclasses
+    plan = dataclasses.replace(base, order=(R(0), R(1), R(0, cache=2), R(1, cache=1, writes_cache=False)))
+
+    def planner(_cfg):
+        return plan
+
+    @dataclass(frozen=True)
+    class LoopCfg(pe.Qwen3Config):
+        pass
+
+    pe.register_architecture("LoopedQwen3", pe.Qwen3Config, planner, replace=True)
+    try:
+        cfg2 = dataclasses.replace(cfg, architecture="LoopedQwen3")
+        eng = pe.Engine.from_random(cfg2, seed=9, dtype="float32", max_cache_tokens=256, max_batch=2)
+        assert sorted(eng.model.cache_requests()) == [0, 1, 2]
+        w = {k: v.float().cpu() for k, v in pe.weights.random_weights(plan, 9, device=DEV).items()}
+        toks = [3, 200, 17, 17, 42, 9, 250, 1, 77]
+        c = cfg.to_dict()
+
+        def plain_looped(tokens):
+            x = w["model.embed_tokens.weight"][tokens]
+            S = len(tokens)
+            kv1 = {}
+
+            def block(x, layer, reuse=None):
+                p = f"model.layers.{layer}"
+                n = plain.rms_norm(x, w[f"{p}.input_layernorm.weight"], c["rms_norm_eps"])
+                f = lambda nm: w[f"{p}.self_attn.{nm}.weight"]
+                q = plain.rms_norm((n @ f("q_proj").T).view(S, 4, 16), f("q_norm"), c["rms_norm_eps"])
+                cos, sin = plain.rope_cos_sin(torch.arange(S), 16, c["rope_theta"])
+                q = plain.rope_rotate_neox(q, cos, sin, 16)
+                if reuse is None:
+                    k = plain.rms_norm((n @ f("k_proj").T).view(S, 2, 16), f("k_norm"), c["rms_norm_eps"])
+                    k = plain.rope_rotate_neox(k, cos, sin, 16)
+                    v = (n @ f("v_proj").T).view(S, 2, 16)
+                    kv1[layer] = (k, v)
+                else:
+                    k, v = reuse
+                a = plain.causal_gqa_attention(q, k, v, 0.25).reshape(S, 64) @ f("o_proj").T
+                h = x + a
+                n2 = plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], c["rms_norm_eps"])
+                return h + plain.swiglu(n2, w[f"{p}.mlp.gate_proj.weight"], w[f"{p}.mlp.up_proj.weight"], w[f"{p}.mlp.down_proj.weight"])
+
+            x = block(x, 0)
+            x = block(x, 1)
+            first_kv1 = kv1[1]
+            x = block(x, 0)
+            x = block(x, 1, reuse=first_kv1)
+            return plain.rms_norm(x, w["model.norm.weight"], c["rms_norm_eps"]) @ w["model.embed_tokens.weight"].T
+
+        s = eng.alloc_slot()
+        lg = [eng.step([pe.StepEntry(s, toks[:6], (0, 5))]).cpu()]
+        for t in toks[6:]:
+            lg.append(eng.step([pe.StepEntry(s, [t], (0,))]).cpu())
+        eng.free_slot(s)
+        ref = plain_looped(toks)
+        assert rel_err(torch.cat(lg), ref[[0, 5, 6, 7, 8]]) < 1e-5
+    finally:
+        pe.config.unregister_architecture("LoopedQwen3")
