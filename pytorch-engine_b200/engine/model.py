@@ -47,6 +47,15 @@ class DecoderModel:
         self.head = _build_part("head", plan.head, weights, runtime)
         runtime.forget_adopted()
 
+    def graph_safe(self) -> bool:
+        """Whether a step may be recorded into a CUDA graph: every part must say so itself
+        (``graph_safe = True``); a part that reads device memory on the host during its forward cannot."""
+        parts = [self.embedding, self.final_norm, self.head, *self.positions.values()]
+        for b in self.blocks:
+            parts.append(b)
+            parts.extend(getattr(b, name) for name in ("mixer_norm", "mixer", "ffn_norm", "ffn") if hasattr(b, name))
+        return all(getattr(p, "graph_safe", False) for p in parts)
+
     def cache_requests(self) -> Dict[int, Optional[CacheRequest]]:
         """Cache entry id -> what the mixer that writes it needs."""
         reqs: Dict[int, Optional[CacheRequest]] = {}

@@ -35,7 +35,7 @@ class ModelRunner:
         self.cache = cache
         self.runtime = model.runtime
         self.pool = BufferPool(self.runtime.device)
-        self.cuda_graphs = bool(cuda_graphs) and self.runtime.is_cuda
+        self.cuda_graphs = bool(cuda_graphs) and self.runtime.is_cuda and model.graph_safe()
         self._graphs: Dict[int, _DecodeGraph] = {}
         self.steps_run = 0
         self.kernel_launch_estimate = 0

@@ -28,6 +28,8 @@ class GQAttention:
     encoding of the plan, or None).  weights: ``q_proj, k_proj, v_proj, o_proj`` and, with qk_norm,
     ``q_norm, k_norm``."""
 
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
     @classmethod
     def weight_decls(cls, params) -> Dict[str, WeightDecl]:
         h, nh, nkv, d = (int(params[k]) for k in ("hidden", "n_heads", "n_kv_heads", "head_dim"))

@@ -14,6 +14,8 @@ from .registry import register
 class PreNormBlock:
     """``h = x + mixer(norm1(x))``; ``out = h + ffn(norm2(h))`` (pygguf_engine/model.py:1025-1042)."""
 
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
     def __init__(self, spec, parts, runtime) -> None:
         self.runtime = runtime
         self.mixer_norm = parts["mixer_norm"]

@@ -15,6 +15,8 @@ class TokenEmbedding:
     """params: ``vocab``, ``hidden``.  weights: ``weight [vocab, hidden]``.  Output: the float32
     residual stream (pygguf_engine/model.py:2237, pygguf_engine/quant_kernels.py:1846-1847)."""
 
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
     @classmethod
     def weight_decls(cls, params) -> Dict[str, WeightDecl]:
         return {"weight": WeightDecl((int(params["vocab"]), int(params["hidden"])), "embedding")}
@@ -35,6 +37,8 @@ class LinearHead:
     """params: ``vocab``, ``hidden``.  weights: ``weight [vocab, hidden]``; a tied head names the
     embedding's tensor and shares its storage (pygguf_engine/model.py:1678-1683, 2206-2214).
     Output: float32 logits."""
+
+    graph_safe = True  # launches only; nothing in forward() waits for the device
 
     @classmethod
     def weight_decls(cls, params) -> Dict[str, WeightDecl]:

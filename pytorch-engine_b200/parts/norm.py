@@ -15,6 +15,8 @@ from .spec import WeightDecl
 class RMSNorm:
     """params: ``dim``, ``eps``.  weights: ``weight [dim]`` (kept in float32)."""
 
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
     @classmethod
     def weight_decls(cls, params) -> Dict[str, WeightDecl]:
         return {"weight": WeightDecl((int(params["dim"]),), "norm")}

@@ -20,6 +20,8 @@ from .spec import WeightDecl
 class RotaryPosition:
     """params: ``rotary_dim`` (even, <= head size), ``theta``, ``max_positions``, ``style`` ("neox")."""
 
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
     fusable_rotary = True
 
     @classmethod

@@ -16,6 +16,8 @@ from .spec import WeightDecl
 class SwiGLU:
     """params: ``hidden``, ``intermediate``.  weights: ``gate_proj, up_proj [I, H]``, ``down_proj [H, I]``."""
 
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
     @classmethod
     def weight_decls(cls, params) -> Dict[str, WeightDecl]:
         h, i = int(params["hidden"]), int(params["intermediate"])

@@ -18,6 +18,23 @@ import torch
 
 
 # --------------------------------------------------------------------------------------------
+# storage precision
+# --------------------------------------------------------------------------------------------
+def stored(x: torch.Tensor, store: Optional[torch.dtype]) -> torch.Tensor:
+    """``x`` as it reads back after being stored in ``store`` (None: float32, nothing happens).
+
+    All arithmetic in this file is float32.  A run in bfloat16 stores its activations in 16 bits
+    between operations, as the reference stores them in float16 (pygguf_engine/model.py:1025 norm
+    output, pygguf_engine/quant_kernels.py:1836 linear output, pygguf_engine/model.py:241 rotated q/k,
+    pygguf_engine/kv_cache.py:861 attention output, pygguf_engine/quant_kernels.py:1474 gated product);
+    ``store=torch.bfloat16`` rounds at those places and nowhere else: the residual stream
+    (pygguf_engine/model.py:1033-1042), softmax, norms' statistics and the logits stay float32.
+    Norm followed by rotation is one computation here and rounds once, after the rotation.
+    """
+    return x if store is None else x.to(store).to(torch.float32)
+
+
+# --------------------------------------------------------------------------------------------
 # parts
 # --------------------------------------------------------------------------------------------
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -104,7 +121,8 @@ def causal_gqa_attention(
     return out
 
 
-def swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+def swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+           store: Optional[torch.dtype] = None) -> torch.Tensor:
     """``(silu(x Wg^T) * (x Wu^T)) Wd^T`` with ``silu(z) = z / (1 + exp(-z))``.
 
     pygguf_engine/model.py:839-846 and pygguf_engine/quant_kernels.py:1467-1475.  The reference's
@@ -112,10 +130,10 @@ def swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: to
     (divide before ``down``, multiply after), so it does not appear in float32.
     """
     x = x.to(torch.float32)
-    gate = x @ w_gate.to(torch.float32).T
-    up = x @ w_up.to(torch.float32).T
-    inter = (gate / (1.0 + torch.exp(-gate))) * up
-    return inter @ w_down.to(torch.float32).T
+    gate = stored(x @ w_gate.to(torch.float32).T, store)
+    up = stored(x @ w_up.to(torch.float32).T, store)
+    inter = stored((gate / (1.0 + torch.exp(-gate))) * up, store)
+    return stored(inter @ w_down.to(torch.float32).T, store)
 
 
 def attention_layer(
@@ -129,6 +147,7 @@ def attention_layer(
     eps: float,
     theta: float,
     window: Optional[int],
+    store: Optional[torch.dtype] = None,
 ) -> torch.Tensor:
     """q/k/v projections, per-head q/k RMSNorm, RoPE, causal GQA attention, output projection.
 
@@ -138,26 +157,27 @@ def attention_layer(
     """
     S = x_normed.shape[0]
     f = lambda name: w[f"{prefix}.self_attn.{name}.weight"].to(torch.float32)
-    q = (x_normed @ f("q_proj").T).view(S, n_heads, head_dim)
-    k = (x_normed @ f("k_proj").T).view(S, n_kv_heads, head_dim)
-    v = (x_normed @ f("v_proj").T).view(S, n_kv_heads, head_dim)
+    q = stored(x_normed @ f("q_proj").T, store).view(S, n_heads, head_dim)
+    k = stored(x_normed @ f("k_proj").T, store).view(S, n_kv_heads, head_dim)
+    v = stored(x_normed @ f("v_proj").T, store).view(S, n_kv_heads, head_dim)
     q = rms_norm(q, f("q_norm"), eps)
     k = rms_norm(k, f("k_norm"), eps)
     cos, sin = rope_cos_sin(torch.arange(S), head_dim, theta)
-    q = rope_rotate_neox(q, cos, sin, head_dim)
-    k = rope_rotate_neox(k, cos, sin, head_dim)
-    o = causal_gqa_attention(q, k, v, 1.0 / math.sqrt(head_dim), window=window)
-    return o.reshape(S, n_heads * head_dim) @ f("o_proj").T
+    q = stored(rope_rotate_neox(q, cos, sin, head_dim), store)
+    k = stored(rope_rotate_neox(k, cos, sin, head_dim), store)
+    o = stored(causal_gqa_attention(q, k, v, 1.0 / math.sqrt(head_dim), window=window), store)
+    return stored(o.reshape(S, n_heads * head_dim) @ f("o_proj").T, store)
 
 
-def decoder_block(x: torch.Tensor, w: Dict[str, torch.Tensor], layer: int, cfg: dict, window: Optional[int]) -> torch.Tensor:
+def decoder_block(x: torch.Tensor, w: Dict[str, torch.Tensor], layer: int, cfg: dict, window: Optional[int],
+                  store: Optional[torch.dtype] = None) -> torch.Tensor:
     """Pre-norm block: ``h = x + attn(norm(x))``; ``out = h + mlp(norm(h))``; residual in float32.
 
     pygguf_engine/model.py:1025-1042.
     """
     p = f"model.layers.{layer}"
     eps = float(cfg["rms_norm_eps"])
-    n = rms_norm(x, w[f"{p}.input_layernorm.weight"], eps)
+    n = stored(rms_norm(x, w[f"{p}.input_layernorm.weight"], eps), store)
     a = attention_layer(
         n, w, p,
         n_heads=cfg["num_attention_heads"],
@@ -166,10 +186,11 @@ def decoder_block(x: torch.Tensor, w: Dict[str, torch.Tensor], layer: int, cfg: 
         eps=eps,
         theta=float(cfg["rope_theta"]),
         window=window,
+        store=store,
     )
     h = x + a
-    n2 = rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], eps)
-    f = swiglu(n2, w[f"{p}.mlp.gate_proj.weight"], w[f"{p}.mlp.up_proj.weight"], w[f"{p}.mlp.down_proj.weight"])
+    n2 = stored(rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], eps), store)
+    f = swiglu(n2, w[f"{p}.mlp.gate_proj.weight"], w[f"{p}.mlp.up_proj.weight"], w[f"{p}.mlp.down_proj.weight"], store)
     return h + f
 
 
@@ -187,8 +208,9 @@ def layer_window(cfg: dict, layer: int) -> Optional[int]:
     return int(cfg["sliding_window"]) if layer >= int(cfg.get("max_window_layers", 0)) else None
 
 
-def forward_logits(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
-    """Logits ``[S, V]`` (float32) at every position of one whole sequence.
+def forward_logits(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int],
+                   store: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Logits ``[S, V]`` (float32) at every position of one whole sequence.  ``store``: see ``stored``.
 
     pygguf_engine/model.py:2235-2305: embedding to float32 2237, blocks 2276-2292, final norm 2189-2192,
     output head 2206-2211 (the embedding table when tied, pygguf_engine/model.py:1678-1683), float32 2214.
@@ -199,8 +221,8 @@ def forward_logits(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int])
     ids = torch.as_tensor(list(tokens), dtype=torch.long)
     x = w["model.embed_tokens.weight"].to(torch.float32)[ids]
     for layer in range(cfg["num_hidden_layers"]):
-        x = decoder_block(x, w, layer, cfg, layer_window(cfg, layer))
-    n = rms_norm(x, w["model.norm.weight"], float(cfg["rms_norm_eps"]))
+        x = decoder_block(x, w, layer, cfg, layer_window(cfg, layer), store)
+    n = stored(rms_norm(x, w["model.norm.weight"], float(cfg["rms_norm_eps"])), store)
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return n @ head.to(torch.float32).T
 

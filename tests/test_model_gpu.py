@@ -17,6 +17,13 @@ KEYS = ["A", "B", "C"]
 DTYPES = ["float32", "bfloat16"]
 
 
+def _ref(cfg, w, toks, dtype):
+    """The plain implementation's logits; for a bfloat16 run it stores its activations in bfloat16 at
+    the places where the engine does (the attention of these test models is sharpened, which turns
+    every rounding of a query or key into a visible change of the softmax weights)."""
+    return plain.forward_logits(cfg, w, toks, store=torch.bfloat16 if dtype == "bfloat16" else None)
+
+
 def _tokens(vocab, n, seed):
     g = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (n,), generator=g).tolist()
@@ -91,10 +98,27 @@ def test_each_request_alone_and_whole(pe, engines, oracles, tmp_path, key, dtype
         toks = _tokens(cfg["vocab_size"], n, seed)
         rp = Replay(pe, eng, tmp_path)
         rp.run([("r", toks, list(range(n)))], end=["r"])
-        ref = plain.forward_logits(cfg, w, toks)
+        ref = _ref(cfg, w, toks, dtype)
         _check(rp.got, {("r", i): ref[i] for i in range(n)}, dtype, f"{key} whole, {n} tokens")
     assert not eng.cache.live_slots
     eng.cache.check()
+
+
+@pytest.mark.parametrize("key", KEYS)
+def test_bfloat16_against_the_float32_implementation(pe, tmp_path_factory, tmp_path, key):
+    """The bfloat16 engine against the plain implementation in pure float32, on plain random weights
+    (attention not sharpened): whole requests, then a few tokens one by one."""
+    from conftest import make_model_folder
+    folder = make_model_folder(pe, tmp_path_factory, key, sharpen=None)
+    cfg, w = plain.load_folder(folder)
+    eng = pe.Engine(folder, dtype="bfloat16", max_cache_tokens=64 * 12, max_batch=4)
+    toks = _tokens(cfg["vocab_size"], 200, 21)
+    rp = Replay(pe, eng, tmp_path)
+    rp.run([("r", toks[:190], list(range(190)))])
+    for i in range(190, 200):
+        rp.run([("r", [toks[i]], [0])], end=["r"] if i == 199 else [])
+    ref = plain.forward_logits(cfg, w, toks)
+    _check(rp.got, {("r", i): ref[i] for i in range(200)}, "bfloat16", f"{key} bfloat16 against float32")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -109,7 +133,7 @@ def test_last_32_tokens_one_by_one(pe, engines, oracles, tmp_path, key, dtype):
         rp.run([("r", toks[:head], [head - 1])])
         for i in range(head, n):
             rp.run([("r", [toks[i]], [0])], end=["r"] if i == n - 1 else [])
-        ref = plain.forward_logits(cfg, w, toks)
+        ref = _ref(cfg, w, toks, dtype)
         _check(rp.got, {("r", i): ref[i] for i in range(head - 1, n)}, dtype, f"{key} last 32 of {n}")
     eng.cache.check()
 
@@ -142,7 +166,7 @@ def test_unequal_batches_one_after_another(pe, engines, oracles, tmp_path, key, 
             rp.run([(rid, [seqs[rid][p + k]], [0]) for rid, p, dec in live],
                    end=[rid for rid, p, dec in live if k == dec - 1])
         for rid, p, dec in plan:
-            ref = plain.forward_logits(cfg, w, seqs[rid])
+            ref = _ref(cfg, w, seqs[rid], dtype)
             for i in range(p - 1, p + dec):
                 want[(rid, i)] = ref[i]
         assert not eng.cache.live_slots
@@ -162,7 +186,7 @@ def test_long_decoding_and_first_tokens(pe, engines, oracles, tmp_path, key, dty
     rp.run([("r", toks[:1], [0])])                         # a sequence's very first token, alone
     for i in range(1, n):
         rp.run([("r", [toks[i]], [0])], end=["r"] if i == n - 1 else [])
-    ref = plain.forward_logits(cfg, w, toks)
+    ref = _ref(cfg, w, toks, dtype)
     _check(rp.got, {("r", i): ref[i] for i in range(n)}, dtype, f"{key} {n} tokens one by one")
     _check({k: v for k, v in rp.got.items() if k[1] < 3}, {("r", i): ref[i] for i in range(3)}, dtype, "first tokens")
 
@@ -198,7 +222,7 @@ def test_greedy_generation_through_the_entry_point(pe, engines, oracles, key, dt
         if r.finish_reason == "length":
             assert r.completion_tokens == 8
         # every chosen token is the plain implementation's argmax, or within rounding of it
-        ref = plain.forward_logits(cfg, w, p + r.token_ids)
+        ref = _ref(cfg, w, p + r.token_ids, dtype)
         scale = float(ref.abs().max())
         for j, tok in enumerate(r.token_ids):
             row = ref[len(p) - 1 + j]
@@ -284,7 +308,7 @@ def test_trace_run_program(pe, model_folders, oracles, tmp_path, dtype):
     assert sorted(os.listdir(out)) == ["0.f32", "1.f32", "2.f32", "7.f32", "8.f32"]
     V = cfg["vocab_size"]
     read = lambda s: torch.frombuffer(bytearray(open(out / f"{s}.f32", "rb").read()), dtype=torch.float32).view(-1, V)
-    ra, rb = plain.forward_logits(cfg, w, a), plain.forward_logits(cfg, w, b)
+    ra, rb = _ref(cfg, w, a, dtype), _ref(cfg, w, b, dtype)
     got = {("a", 0): read(0)[0], ("a", 69): read(0)[1], ("b", 17): read(0)[2], ("a", 70): read(1)[0],
            ("a", 71): read(2)[0], ("b", 19): read(2)[1], ("a", 73): read(7)[0], ("c", 19): read(8)[0]}
     assert read(0).shape == (3, V) and read(1).shape == (1, V)
