@@ -389,3 +389,66 @@ extern "C" int pe_attention_generic(int dtype, int decode, const void* q, long l
   if (dtype == PE_BF16) return pe::dispatch<__nv_bfloat16>(a, n_seqs, max_q, decode != 0, stream);
   return PE_ERR_UNSUPPORTED_DTYPE;
 }
+
+// ---- the entry point that allocates nothing (see attention_noalloc.h) ----------------------------
+#include "attention_noalloc.h"
+
+#include <mutex>
+
+namespace pe {
+
+// Scratch for the partial results, inside the library image.  In host code this name is only a
+// handle for the runtime's symbol table, never a device address: the address is looked up below.
+static __device__ __align__(256) float g_noalloc_scratch[PE_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+static float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+static std::mutex g_noalloc_mutex;
+
+// Device address of the array on the current device; looked up once per device.
+static int noalloc_scratch_address(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return PE_ERR_BAD_ARGUMENT;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (p == nullptr) return PE_ERR_BAD_ARGUMENT;
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return PE_OK;
+}
+
+}  // namespace pe
+
+extern "C" int pe_attention_decode_noalloc(int dtype, const void* q, long long q_ld, void* out, long long out_ld,
+                                           int n_seqs, int n_heads, int n_kv_heads, int head_dim, float scale,
+                                           int window, const int* seq_qstart, const int* seq_past, const int* seq_slot,
+                                           const int* page_table, int table_stride, int num_pages, const void* k_pages,
+                                           const void* v_pages, int split_keys, int max_splits, int* status,
+                                           cudaStream_t stream) {
+  if (n_seqs <= 0) return PE_OK;
+  if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || n_heads % n_kv_heads) return PE_ERR_BAD_ARGUMENT;
+  if (split_keys <= 0 || split_keys % pe::kTileKeys || max_splits <= 0) return PE_ERR_BAD_ARGUMENT;
+  const long long need = (long long)n_seqs * n_heads * max_splits * (head_dim + 1);
+  if (need > (long long)PE_NOALLOC_SCRATCH_FLOATS) return PE_ERR_SCRATCH_TOO_LARGE;
+  float* scratch = nullptr;
+  const int e = pe::noalloc_scratch_address(&scratch);
+  if (e != PE_OK) return e;
+  pe::AttnArgs a;
+  a.q = q; a.q_ld = q_ld; a.out = out; a.out_ld = out_ld;
+  a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim; a.scale = scale; a.window = window;
+  a.seq_qstart = seq_qstart; a.seq_past = seq_past; a.seq_slot = seq_slot;
+  a.page_table = page_table; a.table_stride = table_stride; a.num_pages = num_pages;
+  a.k_pages = k_pages; a.v_pages = v_pages; a.status = status;
+  a.split_keys = split_keys; a.max_splits = max_splits;
+  a.part_acc = scratch;
+  a.part_lse = scratch + (size_t)n_seqs * n_heads * max_splits * head_dim;
+  if (dtype == PE_F32) return pe::dispatch<float>(a, n_seqs, 1, true, stream);
+  if (dtype == PE_BF16) return pe::dispatch<__nv_bfloat16>(a, n_seqs, 1, true, stream);
+  return PE_ERR_UNSUPPORTED_DTYPE;
+}

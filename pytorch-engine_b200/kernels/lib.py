@@ -21,6 +21,7 @@ _ERRORS = {
     -3: "unsupported dtype (float32 and bfloat16 only)",
     -4: "the tensor-core kernel refuses this shape",
     -5: "a CUDA driver entry point is missing",
+    -6: "the call needs more scratch than the library's built-in array holds (see csrc/attention_noalloc.h)",
 }
 
 
@@ -46,6 +47,7 @@ _SIGNATURES = {
     "pe_attention_generic": [I, I, P, L, P, L, I, I, I, I, I, F, I, P, P, P, P, I, I, P, P, P, I, I, P, P],
     "pe_sample": [P, L, I, I, F, I, F, F, c_ulonglong, P, P, P, P],
     "pe_repetition_penalty": [P, L, I, I, P, I, P, F, P],
+    "pe_attention_decode_noalloc": [I, P, L, P, L, I, I, I, I, F, I, P, P, P, P, I, I, P, P, I, I, P, P],
 }
 _RESTYPES = {"pe_attention_generic_scratch_floats": (L, [I, I, I, I])}
 
