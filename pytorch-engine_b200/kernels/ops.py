@@ -138,6 +138,27 @@ def attention_generic(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: 
     _count(2 if decode else 1)
 
 
+def attention_mma_supported(dtype: torch.dtype, head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
+    """Whether the tensor-core attention kernels (csrc/attention_mma.cu) take this shape."""
+    return dtype == torch.bfloat16 and bool(library().pe_attention_mma_supported(head_dim, n_heads, n_kv_heads))
+
+
+def attention_mma(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_q: int, n_heads: int,
+                  n_kv_heads: int, head_dim: int, scale: float, window: int, seq_qstart: torch.Tensor,
+                  seq_past: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int,
+                  k_pages: torch.Tensor, v_pages: torch.Tensor, scratch: Optional[torch.Tensor], split_keys: int,
+                  max_splits: int, status: torch.Tensor) -> None:
+    """Same contract as ``attention_generic``, bfloat16 only, head sizes 64 and 128, groups up to 16."""
+    _need(q.stride(-1) == 1 and out.stride(-1) == 1, "attention: rows must be contiguous")
+    _need(q.dtype == out.dtype == k_pages.dtype == torch.bfloat16, "attention_mma: bfloat16 tensors only")
+    check(library().pe_attention_mma(
+        1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), n_seqs, max_q, n_heads, n_kv_heads,
+        head_dim, float(scale), int(window), _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot), _ptr(page_table),
+        page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages), _ptr(scratch), split_keys, max_splits,
+        _ptr(status), _stream()), "attention_mma")
+    _count(2 if decode else 1)
+
+
 def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float, seed: int,
            row_request: torch.Tensor, row_step: torch.Tensor, out_tokens: torch.Tensor) -> None:
     _need(logits.dtype == torch.float32 and logits.stride(-1) == 1, "sample: float32 logits with contiguous rows")

@@ -76,6 +76,10 @@ class GQAttention:
             if not getattr(self.position, "fusable_rotary", False):
                 raise ValueError(f"position encoding {name!r} cannot be fused into attention (needs tables())")
         self.qkv_dim = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
+        # tensor-core kernels where they take the shape (bfloat16, head size 64 or 128, group <= 16);
+        # the generic float32-arithmetic kernels otherwise
+        self.use_mma = runtime.is_cuda and ops.attention_mma_supported(runtime.dtype, self.head_dim, self.n_heads,
+                                                                       self.n_kv_heads)
 
     def forward(self, x: torch.Tensor, ctx, view, writes_cache: bool = True) -> torch.Tensor:
         rt = self.runtime
@@ -107,7 +111,8 @@ class GQAttention:
                 "attn.scratch",
                 (ops.attention_generic_scratch_floats(ctx.n_seqs, self.n_heads, self.head_dim, max_splits),),
                 torch.float32)
-        ops.attention_generic(
+        kernel = ops.attention_mma if self.use_mma else ops.attention_generic
+        kernel(
             ctx.decode, q, out, ctx.n_seqs, ctx.max_q, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
             self.window, ctx.seq_qstart, ctx.seq_past, ctx.seq_slot, view.page_table, view.num_pages, view.k_pages,
             view.v_pages, scratch, SPLIT_KEYS, max_splits, self.runtime.status)

@@ -48,8 +48,13 @@ TEST_CONFIGS = {
               num_key_value_heads=5, head_dim=48, intermediate_size=176, vocab_size=515, rope_theta=500000.0,
               rms_norm_eps=3e-6, tie_word_embeddings=False, max_position_embeddings=512,
               use_sliding_window=True, sliding_window=100, layer_types=["sliding_attention"], eos_token_id=[7, 9]),
+    # D has a head size that the tensor-core attention kernels take (64), a group of 4 and a window
+    "D": dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=112, num_attention_heads=8,
+              num_key_value_heads=2, head_dim=64, intermediate_size=304, vocab_size=300, rope_theta=100000.0,
+              rms_norm_eps=2e-6, tie_word_embeddings=False, max_position_embeddings=1024,
+              use_sliding_window=True, sliding_window=70, max_window_layers=1),
 }
-TEST_SEEDS = {"A": 0, "B": 1, "C": 2}
+TEST_SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
 
 
 def make_model_folder(pe, tmp_path_factory, key, sharpen=None):

@@ -268,6 +268,91 @@ def test_attention_finds_a_far_key(ops, decode, dtype):
         assert torch.allclose(got[h], v_far[h // 2], atol=1e-4 if dtype == torch.float32 else 2e-2)
 
 
+MMA_SHAPES = [(8, 2, 64), (32, 8, 128), (16, 1, 128), (3, 3, 64), (6, 2, 128), (10, 2, 64)]
+
+
+@pytest.mark.parametrize("nh,nkv,d", MMA_SHAPES)
+@pytest.mark.parametrize("window", [0, 37, 150])
+def test_attention_mma_prefill(ops, nh, nkv, d, window):
+    torch.manual_seed(15)
+    dtype = torch.bfloat16
+    assert ops.attention_mma_supported(dtype, d, nh, nkv)
+    lens = [200, 1, 77, 64, 130]
+    pasts = [0, 0, 50, 0, 127]            # the third and the last sequence continue earlier chunks
+    q_lens = [L - p for L, p in zip(lens, pasts)]
+    ps = PagedSetup(lens, nkv, d, dtype, seed=15, key_scale=2.0)
+    N = sum(q_lens)
+    ld = nh * d + 2 * nkv * d             # q rows inside a fused q|k|v buffer
+    q_all = torch.randn(N, ld, device=DEV).to(dtype)
+    out = torch.zeros(N, nh * d, device=DEV, dtype=dtype)
+    qstart = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    past_t = torch.tensor(pasts, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    st = _status()
+    ops.attention_mma(False, q_all, out, len(lens), max(q_lens), nh, nkv, d, scale, window, qstart, past_t,
+                      ps.seq_slot, ps.table, ps.num_pages, ps.k_pages, ps.v_pages, None, 0, 0, st)
+    assert st.tolist()[0] == 0
+    qs, o = [], 0
+    for n in q_lens:
+        qs.append(q_all[o:o + n, : nh * d].cpu().view(n, nh, d)); o += n
+    want = _plain_attention(ps, qs, pasts, nh, scale, window or None)
+    assert rel_err(out.float().cpu().view(N, nh, d), want) < ATT_TOL[dtype]
+
+
+@pytest.mark.parametrize("nh,nkv,d", MMA_SHAPES)
+@pytest.mark.parametrize("window", [0, 300])
+def test_attention_mma_decode(ops, nh, nkv, d, window):
+    torch.manual_seed(16)
+    dtype = torch.bfloat16
+    lens = [1, 700, 256, 257, 33, 64, 65, 513]
+    pasts = [L - 1 for L in lens]
+    ps = PagedSetup(lens, nkv, d, dtype, seed=16, key_scale=2.0)
+    B = len(lens)
+    ld = nh * d + 2 * nkv * d
+    q_all = torch.randn(B, ld, device=DEV).to(dtype)
+    out = torch.zeros(B, nh * d, device=DEV, dtype=dtype)
+    qstart = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    past_t = torch.tensor(pasts, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    split_keys, max_splits = 256, 5
+    scratch = torch.full((ops.attention_generic_scratch_floats(B, nh, d, max_splits),), float("nan"), device=DEV)
+    st = _status()
+    ops.attention_mma(True, q_all, out, B, 1, nh, nkv, d, scale, window, qstart, past_t, ps.seq_slot, ps.table,
+                      ps.num_pages, ps.k_pages, ps.v_pages, scratch, split_keys, max_splits, st)
+    assert st.tolist()[0] == 0
+    qs = [q_all[b: b + 1, : nh * d].cpu().view(1, nh, d) for b in range(B)]
+    want = _plain_attention(ps, qs, pasts, nh, scale, window or None)
+    assert rel_err(out.float().cpu().view(B, nh, d), want) < ATT_TOL[dtype]
+
+
+@pytest.mark.parametrize("decode", [False, True])
+def test_attention_mma_finds_a_far_key_and_ignores_what_lies_beyond_the_length(ops, decode):
+    nh, nkv, d = 8, 2, 128
+    dtype = torch.bfloat16
+    L, far = 650, 13
+    ps = PagedSetup([L], nkv, d, dtype, seed=17, key_scale=0.05)
+    probe = torch.randn(d)
+    probe = probe / probe.norm() * 12.0
+    q = probe.repeat(nh).view(1, nh * d)
+    page = int(ps.table[ps.slots[0], far // 64])
+    ps.k_pages[page, :, far % 64] = (probe * 2.0).to(DEV, dtype)
+    # the row after the sequence's last key matches even better and must not be seen; its value is NaN
+    last_page = int(ps.table[ps.slots[0], L // 64])
+    ps.k_pages[last_page, :, L % 64] = (probe * 4.0).to(DEV, dtype)
+    ps.v_pages[last_page, :, L % 64] = float("nan")
+    out = torch.zeros(1, nh * d, device=DEV, dtype=dtype)
+    qstart = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    past_t = torch.tensor([L - 1], dtype=torch.int32, device=DEV)
+    scratch = torch.zeros(ops.attention_generic_scratch_floats(1, nh, d, 3), device=DEV)
+    ops.attention_mma(decode, q.to(DEV, dtype), out, 1, 1, nh, nkv, d, 1 / math.sqrt(d), 0, qstart, past_t, ps.seq_slot,
+                      ps.table, ps.num_pages, ps.k_pages, ps.v_pages, scratch if decode else None,
+                      256 if decode else 0, 3 if decode else 0, _status())
+    v_far = ps.v_pages[page, :, far % 64].float().cpu()
+    got = out.float().cpu().view(nh, d)
+    for h in range(nh):
+        assert torch.allclose(got[h], v_far[h // 4], atol=2e-2)
+
+
 def test_sampler_greedy_and_ties(ops):
     torch.manual_seed(8)
     logits = torch.randn(6, 1000, device=DEV)

@@ -13,7 +13,7 @@ import plain_qwen3 as plain
 from conftest import ROOT, TEST_CONFIGS, TOL, rel_err
 
 pytestmark = pytest.mark.gpu
-KEYS = ["A", "B", "C"]
+KEYS = ["A", "B", "C", "D"]
 DTYPES = ["float32", "bfloat16"]
 
 
