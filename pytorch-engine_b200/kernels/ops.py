@@ -159,6 +159,27 @@ def attention_mma(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: int,
     _count(2 if decode else 1)
 
 
+def gemm_smallm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether csrc/gemm_smallm.cu takes ``x [M, K] @ weight [N, K]^T``: bfloat16, M <= 16, K % 8 == 0."""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] <= 16
+            and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.is_contiguous())
+
+
+def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, pair_offset: int = 0) -> None:
+    """``out[M, N] = x @ weight^T`` (out bfloat16 or float32).  With ``pair_offset`` = I the weight holds
+    gate rows then up rows and ``out[M, I] = silu(x @ gate^T) * (x @ up^T)``."""
+    _need(gemm_smallm_supported(x, weight), "gemm_smallm: needs bfloat16, M <= 16, K % 8 == 0, contiguous rows")
+    _need(out.stride(-1) == 1 and out.dtype in (torch.bfloat16, torch.float32), "gemm_smallm: out bfloat16 or float32")
+    m, k = x.shape
+    n = out.shape[1]
+    _need(weight.shape[1] == k and weight.shape[0] == (2 * n if pair_offset else n) and out.shape[0] == m,
+          "gemm_smallm: shapes do not match")
+    _need(pair_offset in (0, n), "gemm_smallm: pair_offset must be 0 or the output width")
+    check(library().pe_gemm_smallm(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), out.stride(0), m, n, k,
+                                   1 if out.dtype == torch.float32 else 0, pair_offset, _stream()), "gemm_smallm")
+    _count(1)
+
+
 def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float, seed: int,
            row_request: torch.Tensor, row_step: torch.Tensor, out_tokens: torch.Tensor) -> None:
     _need(logits.dtype == torch.float32 and logits.stride(-1) == 1, "sample: float32 logits with contiguous rows")

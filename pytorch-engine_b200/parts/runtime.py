@@ -12,7 +12,7 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
-from ..kernels import KernelError
+from ..kernels import KernelError, ops
 
 STATUS_MESSAGES = {
     1: "a token id is outside the embedding table (token row {0}, id {1}, vocabulary {2})",
@@ -32,7 +32,9 @@ class Runtime:
         self.is_cuda = self.device.type == "cuda"
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._adopted: Dict[Tuple[int, torch.dtype], torch.Tensor] = {}
-        self.gemm_backend = None  # set by kernels that take over matrix products (see parts/linear.py)
+        self.gemm_backend = None  # a callable (x, weight, out, out_dtype) -> tensor or None that takes over products
+        self.own_small_gemm = True  # products with few rows run on csrc/gemm_smallm.cu
+        self.small_gemm_rows = 8    # up to this many rows (measured: beyond it the library product is faster)
 
     # ---- weights -------------------------------------------------------------------------
     def adopt(self, tensor: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -58,6 +60,10 @@ class Runtime:
             msg = STATUS_MESSAGES.get(s[0], "kernel status {0}").format(*s[1:])
             raise KernelError(f"a kernel reported an error during the step: {msg}")
 
+    def takes_small_gemm(self, x: torch.Tensor, weight: torch.Tensor) -> bool:
+        return (self.own_small_gemm and x.dim() == 2 and x.shape[0] <= self.small_gemm_rows
+                and ops.gemm_smallm_supported(x, weight))
+
     # ---- matrix product ----------------------------------------------------------------------
     def linear(self, x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -68,6 +74,12 @@ class Runtime:
             y = self.gemm_backend(x, weight, out, out_dtype)
             if y is not None:
                 return y
+        if self.takes_small_gemm(x, weight):
+            # a handful of rows: the package's weight-streaming kernel (csrc/gemm_smallm.cu)
+            if out is None:
+                out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
+            ops.gemm_smallm(x, weight, out)
+            return out
         if x.dtype == torch.float32:
             prev = torch.backends.cuda.matmul.allow_tf32
             if prev:

@@ -33,10 +33,14 @@ class SwiGLU:
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         rt = self.runtime
         n = x.shape[0]
-        gu = ctx.buffer("ffn.gate_up", (n, 2 * self.intermediate), rt.dtype)
-        rt.linear(x, self.gate_up, out=gu)
         act = ctx.buffer("ffn.act", (n, self.intermediate), rt.dtype)
-        ops.silu_mul(gu, act)
+        if rt.takes_small_gemm(x, self.gate_up):
+            # few rows: gate|up product with silu(gate) * up in its epilogue
+            ops.gemm_smallm(x, self.gate_up, act, pair_offset=self.intermediate)
+        else:
+            gu = ctx.buffer("ffn.gate_up", (n, 2 * self.intermediate), rt.dtype)
+            rt.linear(x, self.gate_up, out=gu)
+            ops.silu_mul(gu, act)
         delta = ctx.buffer("ffn.delta", (n, self.hidden), rt.dtype)
         rt.linear(act, self.down, out=delta)
         return delta

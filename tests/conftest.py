@@ -75,11 +75,17 @@ def make_model_folder(pe, tmp_path_factory, key, sharpen=None):
     return folder
 
 
+# How much the q-norm weights are scaled.  Sharper attention shows a wrong key better, and it
+# amplifies every rounding of a query or key by the same factor: float32 runs take 6, bfloat16 runs 3.
+SHARPEN = {"float32": 6.0, "bfloat16": 3.0}
+
+
 @pytest.fixture(scope="session")
 def model_folders(pe, tmp_path_factory):
-    """{key: folder} of the three test models, attention sharpened (random weights alone give nearly
+    """{dtype: {key: folder}} of the test models, attention sharpened (random weights alone give nearly
     uniform attention, which would hide a wrong key)."""
-    return {k: make_model_folder(pe, tmp_path_factory, k, sharpen=6.0) for k in TEST_CONFIGS}
+    return {dt: {k: make_model_folder(pe, tmp_path_factory, k, sharpen=f) for k in TEST_CONFIGS}
+            for dt, f in SHARPEN.items()}
 
 
 def rel_err(got: torch.Tensor, ref: torch.Tensor) -> float:

@@ -353,6 +353,51 @@ def test_attention_mma_finds_a_far_key_and_ignores_what_lies_beyond_the_length(o
         assert torch.allclose(got[h], v_far[h // 4], atol=2e-2)
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(16, 64), (100, 80), (515, 200), (4096, 4096), (1000, 12288), (48, 8)])
+def test_gemm_smallm(ops, M, N, K):
+    torch.manual_seed(20)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.5).to(torch.bfloat16)
+    want = x.float().cpu() @ w.float().cpu().T
+    out32 = torch.full((M, N), float("nan"), device=DEV)
+    ops.gemm_smallm(x, w, out32)
+    assert rel_err(out32.cpu(), want) < 2e-5
+    out16 = torch.zeros(M, N + 8, device=DEV, dtype=torch.bfloat16)[:, :N]      # a row stride larger than N
+    ops.gemm_smallm(x, w, out16)
+    assert rel_err(out16.float().cpu(), want) < KTOL[torch.bfloat16]
+    # x as rows of a wider buffer
+    wide = torch.randn(M, K + 24, device=DEV).to(torch.bfloat16)
+    ops.gemm_smallm(wide[:, :K], w, out32)
+    assert rel_err(out32.cpu(), wide[:, :K].float().cpu() @ w.float().cpu().T) < 2e-5
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("I,K", [(176, 80), (200, 96), (3072, 1024), (24, 4096)])
+def test_gemm_smallm_with_the_gate_fused(ops, M, I, K):
+    torch.manual_seed(21)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, device=DEV) * (2.0 / K ** 0.5)).to(torch.bfloat16)
+    gu = x.float().cpu() @ w.float().cpu().T
+    g, u = gu[:, :I], gu[:, I:]
+    want = g / (1 + torch.exp(-g)) * u
+    out = torch.zeros(M, I, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_smallm(x, w, out, pair_offset=I)
+    assert rel_err(out.float().cpu(), want) < KTOL[torch.bfloat16]
+    out32 = torch.zeros(M, I, device=DEV)
+    ops.gemm_smallm(x, w, out32, pair_offset=I)
+    assert rel_err(out32.cpu(), want) < 2e-5
+
+
+def test_gemm_smallm_refuses_what_it_does_not_take(pe, ops):
+    x = torch.zeros(17, 64, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(32, 64, device=DEV, dtype=torch.bfloat16)
+    assert not ops.gemm_smallm_supported(x, w)
+    assert not ops.gemm_smallm_supported(x[:4, :60], w[:, :60].contiguous())
+    with pytest.raises(pe.kernels.KernelError):
+        ops.gemm_smallm(x, w, torch.zeros(17, 32, device=DEV))
+
+
 def test_sampler_greedy_and_ties(ops):
     torch.manual_seed(8)
     logits = torch.randn(6, 1000, device=DEV)

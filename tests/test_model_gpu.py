@@ -29,9 +29,24 @@ def _tokens(vocab, n, seed):
     return torch.randint(0, vocab, (n,), generator=g).tolist()
 
 
+class _Oracles:
+    """(config, weights) of a test model; ``oracles[key]`` is the float32 variant, ``oracles[key, dtype]``
+    the one whose attention is sharpened as that dtype's runs are."""
+
+    def __init__(self, folders):
+        self.folders = folders
+        self.loaded = {}
+
+    def __getitem__(self, item):
+        key, dtype = item if isinstance(item, tuple) else (item, "float32")
+        if (key, dtype) not in self.loaded:
+            self.loaded[key, dtype] = plain.load_folder(self.folders[dtype][key])
+        return self.loaded[key, dtype]
+
+
 @pytest.fixture(scope="module")
 def oracles(model_folders):
-    return {k: plain.load_folder(f) for k, f in model_folders.items()}
+    return _Oracles(model_folders)
 
 
 @pytest.fixture(scope="module")
@@ -43,7 +58,7 @@ def engines(pe, model_folders):
         if ident not in made:
             args = dict(dtype=dtype, max_cache_tokens=64 * 40, max_batch=8)
             args.update(kw)
-            made[ident] = pe.Engine(model_folders[key], **args)
+            made[ident] = pe.Engine(model_folders[dtype][key], **args)
         return made[ident]
 
     return get
@@ -92,7 +107,7 @@ def _check(got, oracle_rows, dtype, what):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("key", KEYS)
 def test_each_request_alone_and_whole(pe, engines, oracles, tmp_path, key, dtype):
-    cfg, w = oracles[key]
+    cfg, w = oracles[key, dtype]
     eng = engines(key, dtype)
     for n, seed in [(150, 1), (1, 2), (65, 3), (333, 4)]:
         toks = _tokens(cfg["vocab_size"], n, seed)
@@ -124,7 +139,7 @@ def test_bfloat16_against_the_float32_implementation(pe, tmp_path_factory, tmp_p
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("key", KEYS)
 def test_last_32_tokens_one_by_one(pe, engines, oracles, tmp_path, key, dtype):
-    cfg, w = oracles[key]
+    cfg, w = oracles[key, dtype]
     eng = engines(key, dtype)
     for n, seed in [(33, 5), (100, 6), (290, 7)]:
         toks = _tokens(cfg["vocab_size"], n, seed)
@@ -144,7 +159,7 @@ def test_unequal_batches_one_after_another(pe, engines, oracles, tmp_path, key, 
     """Two batches; in each, prompts of unequal lengths go in together, every request is then fed
     its remaining tokens one per step, and the shorter requests end earlier.  The second batch gets
     the slots and pages that the first gave back."""
-    cfg, w = oracles[key]
+    cfg, w = oracles[key, dtype]
     eng = engines(key, dtype)
     rp = Replay(pe, eng, tmp_path)
     want = {}
@@ -178,7 +193,7 @@ def test_unequal_batches_one_after_another(pe, engines, oracles, tmp_path, key, 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("key", ["A", "B"])
 def test_long_decoding_and_first_tokens(pe, engines, oracles, tmp_path, key, dtype):
-    cfg, w = oracles[key]
+    cfg, w = oracles[key, dtype]
     eng = engines(key, dtype)
     n = 600
     toks = _tokens(cfg["vocab_size"], n, 30)
@@ -193,7 +208,7 @@ def test_long_decoding_and_first_tokens(pe, engines, oracles, tmp_path, key, dty
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_graph_replay_equals_eager_steps(pe, engines, oracles, tmp_path, dtype):
-    cfg, w = oracles["B"]
+    cfg, w = oracles["B", dtype]
     toks = [_tokens(cfg["vocab_size"], 90, 40 + i) for i in range(3)]
     outs = []
     for graphs in (True, False):
@@ -211,7 +226,7 @@ def test_graph_replay_equals_eager_steps(pe, engines, oracles, tmp_path, dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("key", KEYS)
 def test_greedy_generation_through_the_entry_point(pe, engines, oracles, key, dtype):
-    cfg, w = oracles[key]
+    cfg, w = oracles[key, dtype]
     eng = engines(key, dtype)
     prompts = [_tokens(cfg["vocab_size"], n, 50 + n) for n in (5, 9, 13, 70)]
     params = pe.SamplingParams(max_tokens=8, temperature=0.0, top_k=0, top_p=1.0, min_p=0.0)
@@ -290,7 +305,7 @@ def test_cache_too_small_is_an_error_not_a_wrong_result(pe, engines, oracles):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_trace_run_program(pe, model_folders, oracles, tmp_path, dtype):
     """The program itself, as a user runs it: steps on standard input, ``done`` lines, .f32 files."""
-    cfg, w = oracles["B"]
+    cfg, w = oracles["B", dtype]
     a, b = _tokens(cfg["vocab_size"], 75, 90), _tokens(cfg["vocab_size"], 20, 91)
     steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:70], "want": [0, 69]}, {"id": "b", "tokens": b[:18], "want": [17]}], "end": []},
              {"step": 1, "entries": [{"id": "a", "tokens": [a[70]], "want": [0]}, {"id": "b", "tokens": [b[18]], "want": []}], "end": []},
@@ -300,7 +315,7 @@ def test_trace_run_program(pe, model_folders, oracles, tmp_path, dtype):
              {"step": 8, "entries": [{"id": "c", "tokens": b, "want": [19]}], "end": ["c"]}]
     out = tmp_path / "out"
     env = dict(os.environ)
-    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_folders["B"], "--dtype", dtype,
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_folders[dtype]["B"], "--dtype", dtype,
                            "--out", str(out), "--max-tokens", "192"],
                           input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, env=env, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
