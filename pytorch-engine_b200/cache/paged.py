@@ -109,7 +109,8 @@ class PagedCache:
         if r.kind == "kv":
             g.num_pages = pages_for(self.max_tokens)
             g.pool = NumberPool(g.num_pages, "page")
-            g.storage = torch.empty((len(g.entries), 2, g.num_pages, r.kv_heads, PAGE_TOKENS, r.head_dim),
+            # zeros, not uninitialised memory: rows that were never written must hold finite values
+            g.storage = torch.zeros((len(g.entries), 2, g.num_pages, r.kv_heads, PAGE_TOKENS, r.head_dim),
                                     dtype=self.dtype, device=self.device)
             g.page_table = torch.full((self.max_slots, self.table_width), -1, dtype=torch.int32, device=self.device)
         elif r.kind == "state":

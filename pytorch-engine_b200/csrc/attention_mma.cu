@@ -12,14 +12,20 @@
 // ride along in the M dimension of the MMA instead of re-reading K and V.
 //   prefill: a block of 4 warps owns 64 consecutive rows of one (sequence, kv head) and walks the
 //            64-key pages of that sequence up to its last row's position; each warp owns 16 rows.
-//            K/V pages are double-buffered in shared memory with cp.async.
+//            K/V pages are double-buffered in shared memory.
 //   decode:  one token per sequence, so a kv head has `group` rows (<= 16: one MMA row block).  A block
 //            owns one (sequence, kv head, range of `split_keys` keys); its 4 warps each take 16 keys of
 //            every 64-key page and are merged at the end; a second kernel merges the ranges.  Which
 //            keys a partial result covers depends only on the sequence's own length.
-// Shared-memory tiles are [64 keys][head_dim] bfloat16 with the 16-byte chunks of a row XOR-swizzled
-// by (row & 7), which makes both the row-wise (K) and the transposed (V) ldmatrix reads conflict-free.
+// K/V pages travel from the cache to shared memory by TMA (cp.async.bulk.tensor, one elected thread,
+// completion counted on an mbarrier): a page of one kv head is a [64 keys][head_dim] box of a 2-D
+// tensor map over the layer's pages, split into 64-feature (128-byte) sub-tiles with the 128-byte
+// swizzle, i.e. the 16-byte chunks of a row are XOR-ed with (row & 7).  That makes both the row-wise
+// (K) and the transposed (V) ldmatrix reads conflict-free.  Rows of a page beyond the sequence's
+// length are not read as zeros: the cache never holds a non-finite value there (the append kernel
+// clears the rest of a page when it starts one), and their probabilities are exactly zero.
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace pe {
 namespace fa {
@@ -41,13 +47,6 @@ struct Args {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
-  const int sz = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros, nothing is read
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -66,42 +65,53 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// byte offset of 16-byte chunk `chunk` of row `row` in a swizzled [rows][HD] bfloat16 tile
-template <int HD> __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
-  return (uint32_t)(row * (HD * 2) + ((chunk ^ (row & 7)) << 4));
+// byte offset of 16-byte chunk `chunk` of row `row` in a [ROWS][HD] bfloat16 tile stored as
+// HD/64 sub-tiles of [ROWS][64] with the 128-byte swizzle (the layout TMA writes)
+template <int HD, int ROWS = BN> __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+  return (uint32_t)((chunk >> 3) * (ROWS * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-// Start the copy of one page (64 keys of kv head `kvh`) of K and V into a stage.  Rows at or beyond
-// `k_end` (counted from the page's first key `k0`) are zero-filled: the cache holds garbage there.
-template <int HD, int NT>
-__device__ __forceinline__ void load_page(const Args& a, int slot, int kvh, int k0, int k_end, char* stage, int tid) {
+// One elected thread starts the copy of one page (64 keys of kv head `kvh`) of K and V into a stage;
+// `bar` counts the bytes.
+template <int HD>
+__device__ __forceinline__ void issue_page(const Args& a, const CUtensorMap* kmap, const CUtensorMap* vmap, int slot,
+                                           int kvh, int k0, char* stage, uint64_t* bar) {
   const int logical = k0 / BN;
   int page = -1;
   if (logical < a.table_stride) page = a.page_table[(size_t)slot * a.table_stride + logical];
-  const bool ok = page >= 0 && page < a.num_pages;
-  if (!ok && tid == 0) report(a.status, kStatusPageOutOfRange, slot, page, k0);
-  const size_t base = ((size_t)(ok ? page : 0) * a.n_kv_heads + kvh) * BN * HD;
-  const __nv_bfloat16* kp = a.k_pages + base;
-  const __nv_bfloat16* vp = a.v_pages + base;
-  constexpr int CPR = HD / 8;  // chunks per row
-  const uint32_t ks = smem_u32(stage), vs = ks + BN * HD * 2;
-  static_assert((BN * CPR) % NT == 0, "a page is a whole number of rounds of 16-byte copies");
-#pragma unroll
-  for (int j = 0; j < (BN * CPR) / NT; ++j) {
-    const int i = tid + j * NT;
-    const int row = i / CPR, chunk = i % CPR;
-    const bool live = ok && (k0 + row) < k_end;
-    const uint32_t off = tile_off<HD>(row, chunk);
-    cp_async16(ks + off, kp + row * HD + chunk * 8, live);
-    cp_async16(vs + off, vp + row * HD + chunk * 8, live);
+  if (page < 0 || page >= a.num_pages) {
+    report(a.status, kStatusPageOutOfRange, slot, page, k0);
+    page = 0;
   }
+  const int y = (page * a.n_kv_heads + kvh) * BN;
+  tma::mbar_expect_tx(bar, 2 * BN * HD * 2);
+#pragma unroll
+  for (int sub = 0; sub < HD / 64; ++sub) {
+    tma::load_2d(stage + sub * (BN * 128), kmap, sub * 64, y, bar);
+    tma::load_2d(stage + BN * HD * 2 + sub * (BN * 128), vmap, sub * 64, y, bar);
+  }
+}
+
+// A wait ran out: record it, give copies still in flight a last bounded chance to land, and leave.
+__device__ __forceinline__ void give_up(const Args& a, uint64_t* bars, int n_bars, int where) {
+  if (threadIdx.x == 0) report(a.status, kStatusWaitTimedOut, where, blockIdx.x, blockIdx.z);
+  for (int s = 0; s < n_bars; ++s)
+    for (int i = 0; i < 1000; ++i)
+      if (tma::mbar_try_wait(&bars[s], 0) || tma::mbar_try_wait(&bars[s], 1)) break;
+}
+
+__device__ __forceinline__ char* align_1024(char* p) {
+  return reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
 }
 
 // ---- prefill ---------------------------------------------------------------------------------------
 // grid: (row tiles of 64, n_kv_heads, n_seqs); block: 128 threads.
 template <int HD>
-__global__ void __launch_bounds__(128) prefill_kernel(Args a) {
-  extern __shared__ __align__(128) char smem[];
+__global__ void __launch_bounds__(128) prefill_kernel(Args a, const __grid_constant__ CUtensorMap kmap,
+                                                      const __grid_constant__ CUtensorMap vmap) {
+  extern __shared__ char smem_raw[];
+  __shared__ uint64_t bars[2];
+  char* smem = align_1024(smem_raw);
   constexpr int STAGE = 2 * BN * HD * 2;      // K and V tile
   constexpr int KS = HD / 16;                 // k-steps of Q.K^T
   constexpr int NO = HD / 8;                  // n-tiles of the output
@@ -123,8 +133,12 @@ __global__ void __launch_bounds__(128) prefill_kernel(Args a) {
   const int n_tiles = (k_end - k_begin + BN - 1) / BN;
 
   // first K/V page in flight, then stage Q
-  load_page<HD, 128>(a, slot, kvh, k_begin, k_end, smem, tid);
-  cp_async_commit();
+  if (tid == 0) {
+    tma::mbar_init(&bars[0], 1);
+    tma::mbar_init(&bars[1], 1);
+    tma::fence_barrier_init();
+    issue_page<HD>(a, &kmap, &vmap, slot, kvh, k_begin, smem, &bars[0]);
+  }
   constexpr int CPR = HD / 8;
   for (int i = tid; i < 64 * CPR; i += 128) {
     const int r = i / CPR, chunk = i % CPR;
@@ -156,14 +170,13 @@ __global__ void __launch_bounds__(128) prefill_kernel(Args a) {
   for (int it = 0; it < n_tiles; ++it) {
     const int k0 = k_begin + it * BN;
     char* stage = smem + (it & 1) * STAGE;
-    if (it + 1 < n_tiles) {  // next page into the other stage (everyone left it at the end of the last round)
-      load_page<HD, 128>(a, slot, kvh, k0 + BN, k_end, smem + ((it + 1) & 1) * STAGE, tid);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+    // next page into the other stage (everyone left it at the end of the last round)
+    if (tid == 0 && it + 1 < n_tiles)
+      issue_page<HD>(a, &kmap, &vmap, slot, kvh, k0 + BN, smem + ((it + 1) & 1) * STAGE, &bars[(it + 1) & 1]);
+    if (!tma::mbar_wait(&bars[it & 1], (it >> 1) & 1)) {
+      give_up(a, bars, 2, 1);
+      return;
     }
-    __syncthreads();
     const bool skip = (k0 > warp_last_pos) || (a.window > 0 && k0 + BN - 1 <= warp_first_pos - a.window);
     if (!skip) {
       const uint32_t ks_base = smem_u32(stage), vs_base = ks_base + BN * HD * 2;
@@ -260,8 +273,11 @@ __global__ void __launch_bounds__(128) prefill_kernel(Args a) {
 // ---- decode ------------------------------------------------------------------------------------------
 // grid: (max_splits, n_kv_heads, n_seqs); block: 128 threads; STAGES pages in flight.
 template <int HD, int STAGES>
-__global__ void __launch_bounds__(128) decode_split_kernel(Args a) {
-  extern __shared__ __align__(128) char smem[];
+__global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_constant__ CUtensorMap kmap,
+                                                           const __grid_constant__ CUtensorMap vmap) {
+  extern __shared__ char smem_raw[];
+  __shared__ uint64_t bars[STAGES];
+  char* smem = align_1024(smem_raw);
   constexpr int STAGE = 2 * BN * HD * 2;
   constexpr int KS = HD / 16;
   constexpr int NO = HD / 8;
@@ -280,24 +296,27 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a) {
   const int k_first = max(k_lo, win_lo);         // first visible key of this range
   const int k_begin = k_first / BN * BN;
   const int n_tiles = (k_hi - k_begin + BN - 1) / BN;
+  if (tid == 0) {
 #pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < n_tiles) load_page<HD, 128>(a, slot, kvh, k_begin + s * BN, k_hi, smem + s * STAGE, tid);
-    cp_async_commit();
+    for (int s = 0; s < STAGES; ++s) tma::mbar_init(&bars[s], 1);
+    tma::fence_barrier_init();
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s)
+      if (s < n_tiles) issue_page<HD>(a, &kmap, &vmap, slot, kvh, k_begin + s * BN, smem + s * STAGE, &bars[s]);
   }
   constexpr int CPR = HD / 8;
   for (int i = tid; i < 16 * CPR; i += 128) {
     const int r = i / CPR, chunk = i % CPR;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < group) v = *reinterpret_cast<const uint4*>(a.q + (size_t)tq * a.q_ld + (size_t)(kvh * group + r) * HD + chunk * 8);
-    *reinterpret_cast<uint4*>(q_s + tile_off<HD>(r, chunk)) = v;
+    *reinterpret_cast<uint4*>(q_s + tile_off<HD, 16>(r, chunk)) = v;
   }
   __syncthreads();
   uint32_t qf[KS][4];
 #pragma unroll
   for (int ks = 0; ks < KS; ++ks) {
     const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
-    ldmatrix_x4(qf[ks], smem_u32(q_s) + tile_off<HD>(r, ks * 2 + (lane >> 4)));
+    ldmatrix_x4(qf[ks], smem_u32(q_s) + tile_off<HD, 16>(r, ks * 2 + (lane >> 4)));
   }
   float o[NO][4];
 #pragma unroll
@@ -305,12 +324,14 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a) {
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
   for (int it = 0; it < n_tiles; ++it) {
-    // keep STAGES-1 pages in flight
+    // keep STAGES-1 pages in flight (the stage refilled here was released by the last round's barrier)
     const int nxt = it + STAGES - 1;
-    if (nxt < n_tiles) load_page<HD, 128>(a, slot, kvh, k_begin + nxt * BN, k_hi, smem + (nxt % STAGES) * STAGE, tid);
-    cp_async_commit();
-    cp_async_wait<STAGES - 1>();
-    __syncthreads();
+    if (tid == 0 && nxt < n_tiles)
+      issue_page<HD>(a, &kmap, &vmap, slot, kvh, k_begin + nxt * BN, smem + (nxt % STAGES) * STAGE, &bars[nxt % STAGES]);
+    if (!tma::mbar_wait(&bars[it % STAGES], (it / STAGES) & 1)) {
+      give_up(a, bars, STAGES, 2);
+      return;
+    }
     const int k0 = k_begin + it * BN;
     const int key0 = warp * 16;                  // this warp's 16 keys of the page
     if (k0 + key0 < k_hi && k0 + key0 + 15 >= k_first) {
@@ -375,8 +396,6 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a) {
     }
     __syncthreads();
   }
-  cp_async_wait<0>();
-  __syncthreads();
   // merge the four warps (fixed order) through shared memory laid over the stages
   float* ml = reinterpret_cast<float*>(smem);            // [4 warps][16 rows][2]
   float* acc = ml + 4 * 16 * 2;                          // [4 warps][16 rows][HD]
@@ -457,15 +476,20 @@ static int opt_in(K kernel, size_t bytes) {
 template <int HD>
 static int launch(const Args& a, bool decode, int n_seqs, int max_q, cudaStream_t stream) {
   constexpr int STAGE = 2 * BN * HD * 2;
+  CUtensorMap kmap, vmap;
+  const uint64_t rows = (uint64_t)a.num_pages * a.n_kv_heads * BN;
+  int me = tma::make_map_2d_bf16(&kmap, a.k_pages, HD, rows, HD, 64, BN);
+  if (me == 0) me = tma::make_map_2d_bf16(&vmap, a.v_pages, HD, rows, HD, 64, BN);
+  if (me != 0) return me < 0 ? me : PE_ERR_BAD_ARGUMENT;
   if (!decode) {
-    const size_t smem = 2 * STAGE + 64 * HD * 2;
+    const size_t smem = 1024 + 2 * STAGE + 64 * HD * 2;
     auto k = prefill_kernel<HD>;
     int e = opt_in(k, smem);
     if (e) return e;
     const long long tiles = ((long long)max_q * a.group + 63) / 64;
     dim3 grid((unsigned)tiles, a.n_kv_heads, n_seqs);
     if (grid.y > 65535 || grid.z > 65535) return PE_ERR_UNSUPPORTED_SIZE;
-    k<<<grid, 128, smem, stream>>>(a);
+    k<<<grid, 128, smem, stream>>>(a, kmap, vmap);
     PE_LAUNCH_CHECK();
     return PE_OK;
   }
@@ -473,12 +497,13 @@ static int launch(const Args& a, bool decode, int n_seqs, int max_q, cudaStream_
   size_t smem = STAGES * STAGE + 16 * HD * 2;
   const size_t merge = (4 * 16 * 2 + 4 * 16 * HD) * sizeof(float);
   if (merge > smem) smem = merge;
+  smem += 1024;
   auto k = decode_split_kernel<HD, STAGES>;
   int e = opt_in(k, smem);
   if (e) return e;
   dim3 grid(a.max_splits, a.n_kv_heads, n_seqs);
   if (grid.y > 65535 || grid.z > 65535) return PE_ERR_UNSUPPORTED_SIZE;
-  k<<<grid, 128, smem, stream>>>(a);
+  k<<<grid, 128, smem, stream>>>(a, kmap, vmap);
   PE_LAUNCH_CHECK();
   dim3 mgrid(a.n_heads, n_seqs);
   decode_merge_kernel<HD><<<mgrid, HD >= 128 ? 128 : 64, 0, stream>>>(a);

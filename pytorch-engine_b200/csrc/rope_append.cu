@@ -35,6 +35,7 @@ struct RopeAppendArgs {
   const int* token_seq;
   const int* token_pos;
   const int* seq_slot;
+  const int* seq_qstart;   // [n_seqs + 1]
   const int* page_table;   // [slots, table_stride]
   int table_stride, num_pages;
   void* k_pages;           // [num_pages, n_kv_heads, 64, head_dim]
@@ -70,7 +71,24 @@ __global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
         if (lane == 0) report(a.status, kStatusPageOutOfRange, t, page, a.num_pages);
       } else {
         T* base = (T*)(is_k ? a.k_pages : a.v_pages);
-        cache_row = base + (((size_t)page * a.n_kv_heads + kv_head) * kPageTokens + (pos % kPageTokens)) * d;
+        const int off = pos % kPageTokens;
+        cache_row = base + (((size_t)page * a.n_kv_heads + kv_head) * kPageTokens + off) * d;
+        // Rows of a page beyond the sequence's last key must hold finite values (readers multiply them
+        // by a probability of zero): the sequence's last token of this step clears the rest of its page
+        // when it starts the page or ends a multi-token step; later single tokens find it cleared.
+        const int b = a.token_seq[t];
+        const int q_end = a.seq_qstart[b + 1];
+        if (t + 1 == q_end && off + 1 < kPageTokens && (off == 0 || q_end - a.seq_qstart[b] > 1)) {
+          T* rest = cache_row + d;
+          const size_t n = (size_t)(kPageTokens - 1 - off) * d;
+          if ((d * sizeof(T)) % 16 == 0) {
+            uint4* r4 = reinterpret_cast<uint4*>(rest);
+            const size_t n4 = n * sizeof(T) / 16;
+            for (size_t i = lane; i < n4; i += 32) r4[i] = make_uint4(0, 0, 0, 0);
+          } else {
+            for (size_t i = lane; i < n; i += 32) rest[i] = from_f32<T>(0.f);
+          }
+        }
       }
     }
   }
@@ -142,7 +160,7 @@ extern "C" int pe_qk_norm_rope_append(int dtype, void* qkv, long long ld, int n_
                                       int head_dim, const float* q_norm_w, const float* k_norm_w, float eps,
                                       const float* cos_table, const float* sin_table, int rotary_dim, int table_rows,
                                       const int* token_seq, const int* token_pos, const int* seq_slot,
-                                      const int* page_table, int table_stride, int num_pages, void* k_pages,
+                                      const int* seq_qstart, const int* page_table, int table_stride, int num_pages, void* k_pages,
                                       void* v_pages, int write_cache, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return PE_OK;
   if (head_dim <= 0 || n_heads <= 0 || n_kv_heads < 0) return PE_ERR_BAD_ARGUMENT;
@@ -152,7 +170,7 @@ extern "C" int pe_qk_norm_rope_append(int dtype, void* qkv, long long ld, int n_
   a.qkv = qkv; a.ld = ld; a.n_tokens = n_tokens; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.head_dim = head_dim;
   a.q_norm_w = q_norm_w; a.k_norm_w = k_norm_w; a.eps = eps;
   a.cos_table = cos_table; a.sin_table = sin_table; a.rotary_dim = rotary_dim; a.table_rows = table_rows;
-  a.token_seq = token_seq; a.token_pos = token_pos; a.seq_slot = seq_slot;
+  a.token_seq = token_seq; a.token_pos = token_pos; a.seq_slot = seq_slot; a.seq_qstart = seq_qstart;
   a.page_table = page_table; a.table_stride = table_stride; a.num_pages = num_pages;
   a.k_pages = k_pages; a.v_pages = v_pages; a.write_cache = write_cache; a.status = status;
   const int warps = 4;

@@ -43,7 +43,7 @@ _SIGNATURES = {
     "pe_rmsnorm": [I, P, P, P, I, I, F, P],
     "pe_silu_mul": [I, P, P, I, I, P],
     "pe_batch_expand": [P, P, I, P, P, P],
-    "pe_qk_norm_rope_append": [I, P, L, I, I, I, I, P, P, F, P, P, I, I, P, P, P, P, I, I, P, P, I, P, P],
+    "pe_qk_norm_rope_append": [I, P, L, I, I, I, I, P, P, F, P, P, I, I, P, P, P, P, P, I, I, P, P, I, P, P],
     "pe_attention_generic": [I, I, P, L, P, L, I, I, I, I, I, F, I, P, P, P, P, I, I, P, P, P, I, I, P, P],
     "pe_sample": [P, L, I, I, F, I, F, F, c_ulonglong, P, P, P, P],
     "pe_repetition_penalty": [P, L, I, I, P, I, P, F, P],

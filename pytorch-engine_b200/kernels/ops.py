@@ -106,14 +106,14 @@ def qk_norm_rope_append(qkv: torch.Tensor, n_tokens: int, n_heads: int, n_kv_hea
                         q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
                         cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
                         token_seq: torch.Tensor, token_pos: torch.Tensor, seq_slot: torch.Tensor,
-                        page_table: Optional[torch.Tensor], num_pages: int, k_pages: Optional[torch.Tensor],
+                        seq_qstart: torch.Tensor, page_table: Optional[torch.Tensor], num_pages: int, k_pages: Optional[torch.Tensor],
                         v_pages: Optional[torch.Tensor], write_cache: bool, status: torch.Tensor) -> None:
     _need(qkv.stride(-1) == 1, "qk_norm_rope_append: rows of qkv must be contiguous")
     table_rows = 0 if cos is None else cos.shape[0]
     check(library().pe_qk_norm_rope_append(
         dtype_tag(qkv.dtype), _ptr(qkv), qkv.stride(0), n_tokens, n_heads, n_kv_heads, head_dim,
         _ptr(q_norm_w), _ptr(k_norm_w), float(eps), _ptr(cos), _ptr(sin), rotary_dim if cos is not None else 0,
-        table_rows, _ptr(token_seq), _ptr(token_pos), _ptr(seq_slot), _ptr(page_table),
+        table_rows, _ptr(token_seq), _ptr(token_pos), _ptr(seq_slot), _ptr(seq_qstart), _ptr(page_table),
         0 if page_table is None else page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages),
         1 if write_cache else 0, _ptr(status), _stream()), "qk_norm_rope_append")
     _count(1)

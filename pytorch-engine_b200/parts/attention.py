@@ -92,7 +92,7 @@ class GQAttention:
             cos, sin, rotary_dim = self.position.tables()
         ops.qk_norm_rope_append(
             qkv, n, self.n_heads, self.n_kv_heads, self.head_dim, self.q_norm, self.k_norm, self.eps, cos, sin,
-            rotary_dim, ctx.token_seq, ctx.token_pos, ctx.seq_slot, view.page_table, view.num_pages, view.k_pages,
+            rotary_dim, ctx.token_seq, ctx.token_pos, ctx.seq_slot, ctx.seq_qstart, view.page_table, view.num_pages, view.k_pages,
             view.v_pages, writes_cache, rt.status)
         out = ctx.buffer("attn.out", (n, self.n_heads * self.head_dim), rt.dtype)
         self.attend(qkv, out, ctx, view)

@@ -141,10 +141,11 @@ def test_qk_norm_rope_append(ops, dtype, nh, nkv, d, rot):
     token_seq = torch.tensor(sum(([b] * n for b, n in enumerate(q_lens)), []), dtype=torch.int32, device=DEV)
     pos_list = sum(([lens[b] - q_lens[b] + i for i in range(q_lens[b])] for b in range(3)), [])
     token_pos = torch.tensor(pos_list, dtype=torch.int32, device=DEV)
+    qstart = torch.tensor([0, 6, 9, 74], dtype=torch.int32, device=DEV)
     k_before, v_before = ps.k_pages.clone(), ps.v_pages.clone()
     st = _status()
     ops.qk_norm_rope_append(qkv[:, : ld], N, nh, nkv, d, qw, kw, eps, cos, sin, rot, token_seq, token_pos, ps.seq_slot,
-                            ps.table, ps.num_pages, ps.k_pages, ps.v_pages, True, st)
+                            qstart, ps.table, ps.num_pages, ps.k_pages, ps.v_pages, True, st)
     assert st.tolist()[0] == 0
     x = before.float().cpu()
     q_in = x[:, : nh * d].view(N, nh, d)
@@ -165,14 +166,23 @@ def test_qk_norm_rope_append(ops, dtype, nh, nkv, d, rot):
         touched[page, p % 64] = True
         assert rel_err(kp[page, :, p % 64], k_want[t]) < KTOL[dtype]
         assert torch.equal(vp[page, :, p % 64], v_in[t])
-    keep = ~touched
+    # the last token of each multi-token step clears the rest of its page (rows after it hold zeros);
+    # every other row is as before
+    cleared = torch.zeros(ps.num_pages, 64, dtype=torch.bool)
+    for b in range(3):
+        last = lens[b] - 1
+        page = int(ps.table[ps.slots[b], last // 64])
+        cleared[page, last % 64 + 1:] = True
+    keep = ~touched & ~cleared
     assert torch.equal(ps.k_pages.cpu().transpose(1, 2)[keep], k_before.cpu().transpose(1, 2)[keep])
     assert torch.equal(ps.v_pages.cpu().transpose(1, 2)[keep], v_before.cpu().transpose(1, 2)[keep])
+    assert float(ps.k_pages.float().cpu().transpose(1, 2)[cleared].abs().sum()) == 0.0
+    assert float(ps.v_pages.float().cpu().transpose(1, 2)[cleared].abs().sum()) == 0.0
     # write_cache off: q and k are still rewritten, the cache is not
     k_now = ps.k_pages.clone()
     qkv2 = before.clone()
     ops.qk_norm_rope_append(qkv2, N, nh, nkv, d, qw, kw, eps, cos, sin, rot, token_seq, token_pos, ps.seq_slot,
-                            ps.table, ps.num_pages, ps.k_pages, ps.v_pages, False, st)
+                            qstart, ps.table, ps.num_pages, ps.k_pages, ps.v_pages, False, st)
     assert torch.equal(qkv2, qkv) and torch.equal(ps.k_pages, k_now)
 
 
@@ -336,10 +346,11 @@ def test_attention_mma_finds_a_far_key_and_ignores_what_lies_beyond_the_length(o
     q = probe.repeat(nh).view(1, nh * d)
     page = int(ps.table[ps.slots[0], far // 64])
     ps.k_pages[page, :, far % 64] = (probe * 2.0).to(DEV, dtype)
-    # the row after the sequence's last key matches even better and must not be seen; its value is NaN
+    # the row after the sequence's last key matches even better and must not be seen (the cache keeps
+    # such rows finite, see the append kernel; a huge value shows any leak)
     last_page = int(ps.table[ps.slots[0], L // 64])
     ps.k_pages[last_page, :, L % 64] = (probe * 4.0).to(DEV, dtype)
-    ps.v_pages[last_page, :, L % 64] = float("nan")
+    ps.v_pages[last_page, :, L % 64] = 1e30
     out = torch.zeros(1, nh * d, device=DEV, dtype=dtype)
     qstart = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
     past_t = torch.tensor([L - 1], dtype=torch.int32, device=DEV)
