@@ -493,17 +493,21 @@ static int launch(const Args& a, bool decode, int n_seqs, int max_q, cudaStream_
     PE_LAUNCH_CHECK();
     return PE_OK;
   }
-  constexpr int STAGES = 3;
-  size_t smem = STAGES * STAGE + 16 * HD * 2;
-  const size_t merge = (4 * 16 * 2 + 4 * 16 * HD) * sizeof(float);
-  if (merge > smem) smem = merge;
-  smem += 1024;
-  auto k = decode_split_kernel<HD, STAGES>;
-  int e = opt_in(k, smem);
-  if (e) return e;
   dim3 grid(a.max_splits, a.n_kv_heads, n_seqs);
   if (grid.y > 65535 || grid.z > 65535) return PE_ERR_UNSUPPORTED_SIZE;
-  k<<<grid, 128, smem, stream>>>(a, kmap, vmap);
+  auto go = [&](auto kern, int STAGES) -> int {
+    size_t smem = STAGES * STAGE + 16 * HD * 2;
+    const size_t merge = (4 * 16 * 2 + 4 * 16 * HD) * sizeof(float);
+    if (merge > smem) smem = merge;
+    smem += 1024;
+    int e = opt_in(kern, smem);
+    if (e) return e;
+    kern<<<grid, 128, smem, stream>>>(a, kmap, vmap);
+    return 0;
+  };
+  // three stages: two blocks per SM, two pages in flight per block (measured best of 2, 3, 4)
+  const int e = go(decode_split_kernel<HD, 3>, 3);
+  if (e) return e;
   PE_LAUNCH_CHECK();
   dim3 mgrid(a.n_heads, n_seqs);
   decode_merge_kernel<HD><<<mgrid, HD >= 128 ? 128 : 64, 0, stream>>>(a);

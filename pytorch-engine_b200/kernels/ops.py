@@ -180,6 +180,41 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, pair_o
     _count(1)
 
 
+_SM_COUNT = {}
+
+
+def sm_count(device) -> int:
+    idx = torch.device(device).index or 0
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SM_COUNT[idx]
+
+
+def gemm_umma_supported(x: torch.Tensor, weight: torch.Tensor, pair_offset: int = 0) -> bool:
+    """Whether csrc/gemm_umma.cu (tcgen05 + TMA) takes ``x [M, K] @ weight^T``: bfloat16, K % 8 == 0."""
+    if not (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and weight.is_contiguous() and x.data_ptr() % 16 == 0):
+        return False
+    n = weight.shape[0] // 2 if pair_offset else weight.shape[0]
+    return bool(library().pe_gemm_umma_supported(x.shape[0], n, x.shape[1], pair_offset))
+
+
+def gemm_umma(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, status: torch.Tensor, pair_offset: int = 0) -> None:
+    """``out[M, N] = x @ weight^T`` on the tcgen05 tensor cores (out bfloat16 or float32); with
+    ``pair_offset`` = I: ``out[M, I] = silu(x @ gate^T) * (x @ up^T)`` for weight = [gate; up]."""
+    _need(gemm_umma_supported(x, weight, pair_offset), "gemm_umma: needs bfloat16, K % 8 == 0, dense weight rows")
+    _need(out.stride(-1) == 1 and out.dtype in (torch.bfloat16, torch.float32), "gemm_umma: out bfloat16 or float32")
+    m, k = x.shape
+    n = out.shape[1]
+    _need(weight.shape[1] == k and weight.shape[0] == (2 * n if pair_offset else n) and out.shape[0] == m,
+          "gemm_umma: shapes do not match")
+    _need(not pair_offset or out.dtype == torch.bfloat16, "gemm_umma: the fused gate writes bfloat16")
+    check(library().pe_gemm_umma(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), out.stride(0), m, n, k,
+                                 1 if out.dtype == torch.float32 else 0, pair_offset, sm_count(x.device), _ptr(status),
+                                 _stream()), "gemm_umma")
+    _count(1)
+
+
 def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float, seed: int,
            row_request: torch.Tensor, row_step: torch.Tensor, out_tokens: torch.Tensor) -> None:
     _need(logits.dtype == torch.float32 and logits.stride(-1) == 1, "sample: float32 logits with contiguous rows")

@@ -18,7 +18,7 @@ from .linear import fuse_rows
 from .registry import register
 from .spec import CacheRequest, WeightDecl
 
-SPLIT_KEYS = 256  # keys per partial result in decode; a property of the sequence, not of the batch
+SPLIT_KEYS = 512  # keys per partial result in decode; a property of the sequence, not of the batch
 
 
 @register("mixer", "attention")

@@ -35,6 +35,10 @@ class Runtime:
         self.gemm_backend = None  # a callable (x, weight, out, out_dtype) -> tensor or None that takes over products
         self.own_small_gemm = True  # products with few rows run on csrc/gemm_smallm.cu
         self.small_gemm_rows = 8    # up to this many rows (measured: beyond it the library product is faster)
+        # products with many rows run on csrc/gemm_umma.cu (tcgen05 + TMA); in between, and for shapes it
+        # refuses, the library product stands (measured: with fewer rows too few tiles exist to fill the SMs)
+        self.own_large_gemm = True
+        self.large_gemm_rows = 1024
 
     # ---- weights -------------------------------------------------------------------------
     def adopt(self, tensor: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -64,6 +68,11 @@ class Runtime:
         return (self.own_small_gemm and x.dim() == 2 and x.shape[0] <= self.small_gemm_rows
                 and ops.gemm_smallm_supported(x, weight))
 
+    def takes_large_gemm(self, x: torch.Tensor, weight: torch.Tensor, pair_offset: int = 0) -> bool:
+        rows = 9 if pair_offset else self.large_gemm_rows   # the fused gate wins at every size above the small kernel's
+        return (self.own_large_gemm and x.dim() == 2 and x.shape[0] >= rows
+                and ops.gemm_umma_supported(x, weight, pair_offset))
+
     # ---- matrix product ----------------------------------------------------------------------
     def linear(self, x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -74,6 +83,11 @@ class Runtime:
             y = self.gemm_backend(x, weight, out, out_dtype)
             if y is not None:
                 return y
+        if self.takes_large_gemm(x, weight):
+            if out is None:
+                out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
+            ops.gemm_umma(x, weight, out, self.status)
+            return out
         if self.takes_small_gemm(x, weight):
             # a handful of rows: the package's weight-streaming kernel (csrc/gemm_smallm.cu)
             if out is None:
