@@ -113,6 +113,8 @@ __device__ __forceinline__ void fold_tile(const float* qs /*[kGT][d]*/, const fl
 template <typename T, int DPL>
 __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a) {
   extern __shared__ float smem[];
+  pdl_wait();
+  pdl_launch_dependents();
   constexpr int W = 8;
   const int d = a.head_dim;
   float* Ks = smem;                          // [32][d+1]
@@ -182,6 +184,8 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a) {
 template <typename T, int DPL, int NW>
 __global__ void __launch_bounds__(NW * 32) attn_decode_split_kernel(AttnArgs a) {
   extern __shared__ float smem[];
+  pdl_wait();
+  pdl_launch_dependents();
   const int d = a.head_dim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int per_warp = kTileKeys * (d + 1) + kTileKeys * d;
@@ -266,6 +270,8 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_split_kernel(AttnArgs a) 
 // grid: (n_heads, n_seqs); merges the ranges that the split kernel wrote for this sequence.
 template <typename T>
 __global__ void attn_decode_combine_kernel(AttnArgs a) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.y, h = blockIdx.x;
   const int d = a.head_dim;
   const int t = a.seq_qstart[b];
@@ -314,7 +320,7 @@ static int launch_prefill(const AttnArgs& a, int n_seqs, int max_q, cudaStream_t
   const int group = a.n_heads / a.n_kv_heads;
   dim3 grid((max_q + 7) / 8, a.n_kv_heads * ((group + kGT - 1) / kGT), n_seqs);
   if (grid.y > 65535 || grid.z > 65535) return PE_ERR_UNSUPPORTED_SIZE;
-  k<<<grid, 256, smem, stream>>>(a);
+  pe::launch(k, grid, 256, smem, stream, a);
   PE_LAUNCH_CHECK();
   return PE_OK;
 }
@@ -330,10 +336,10 @@ static int launch_decode(const AttnArgs& a, int n_seqs, cudaStream_t stream) {
   const int group = a.n_heads / a.n_kv_heads;
   dim3 grid(a.max_splits, a.n_kv_heads * ((group + kGT - 1) / kGT), n_seqs);
   if (grid.y > 65535 || grid.z > 65535) return PE_ERR_UNSUPPORTED_SIZE;
-  k<<<grid, NW * 32, smem, stream>>>(a);
+  pe::launch(k, grid, NW * 32, smem, stream, a);
   PE_LAUNCH_CHECK();
   dim3 cgrid(a.n_heads, n_seqs);
-  attn_decode_combine_kernel<T><<<cgrid, 128, 0, stream>>>(a);
+  pe::launch(attn_decode_combine_kernel<T>, cgrid, 128, 0, stream, a);
   PE_LAUNCH_CHECK();
   return PE_OK;
 }

@@ -111,6 +111,8 @@ __global__ void __launch_bounds__(128) prefill_kernel(Args a, const __grid_const
                                                       const __grid_constant__ CUtensorMap vmap) {
   extern __shared__ char smem_raw[];
   __shared__ uint64_t bars[2];
+  pdl_wait();
+  pdl_launch_dependents();
   char* smem = align_1024(smem_raw);
   constexpr int STAGE = 2 * BN * HD * 2;      // K and V tile
   constexpr int KS = HD / 16;                 // k-steps of Q.K^T
@@ -277,6 +279,7 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
                                                            const __grid_constant__ CUtensorMap vmap) {
   extern __shared__ char smem_raw[];
   __shared__ uint64_t bars[STAGES];
+  pdl_wait();
   char* smem = align_1024(smem_raw);
   constexpr int STAGE = 2 * BN * HD * 2;
   constexpr int KS = HD / 16;
@@ -396,6 +399,7 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
     }
     __syncthreads();
   }
+  pdl_launch_dependents();
   // merge the four warps (fixed order) through shared memory laid over the stages
   float* ml = reinterpret_cast<float*>(smem);            // [4 warps][16 rows][2]
   float* acc = ml + 4 * 16 * 2;                          // [4 warps][16 rows][HD]
@@ -436,6 +440,8 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
 // grid: (n_heads, n_seqs): merge the ranges of one (sequence, head) (pygguf_engine/kv_cache.py:273-282).
 template <int HD>
 __global__ void decode_merge_kernel(Args a) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.y, h = blockIdx.x;
   const int tq = a.seq_qstart[b];
   const int len = a.seq_past[b] + 1;
@@ -489,7 +495,7 @@ static int launch(const Args& a, bool decode, int n_seqs, int max_q, cudaStream_
     const long long tiles = ((long long)max_q * a.group + 63) / 64;
     dim3 grid((unsigned)tiles, a.n_kv_heads, n_seqs);
     if (grid.y > 65535 || grid.z > 65535) return PE_ERR_UNSUPPORTED_SIZE;
-    k<<<grid, 128, smem, stream>>>(a, kmap, vmap);
+    pe::launch(k, grid, 128, smem, stream, a, kmap, vmap);
     PE_LAUNCH_CHECK();
     return PE_OK;
   }
@@ -502,7 +508,7 @@ static int launch(const Args& a, bool decode, int n_seqs, int max_q, cudaStream_
     smem += 1024;
     int e = opt_in(kern, smem);
     if (e) return e;
-    kern<<<grid, 128, smem, stream>>>(a, kmap, vmap);
+    pe::launch(kern, grid, 128, smem, stream, a, kmap, vmap);
     return 0;
   };
   // three stages: two blocks per SM, two pages in flight per block (measured best of 2, 3, 4)
@@ -510,7 +516,7 @@ static int launch(const Args& a, bool decode, int n_seqs, int max_q, cudaStream_
   if (e) return e;
   PE_LAUNCH_CHECK();
   dim3 mgrid(a.n_heads, n_seqs);
-  decode_merge_kernel<HD><<<mgrid, HD >= 128 ? 128 : 64, 0, stream>>>(a);
+  pe::launch(decode_merge_kernel<HD>, mgrid, HD >= 128 ? 128 : 64, 0, stream, a);
   PE_LAUNCH_CHECK();
   return PE_OK;
 }

@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace pe {
 
@@ -31,6 +32,45 @@ __device__ __forceinline__ void report(int* status, int code, int a = 0, int b =
     status[2] = b;
     status[3] = c;
   }
+}
+
+// ---- programmatic dependent launch -------------------------------------------------------------
+// Every kernel of this library is launched so that it may start while its predecessor in the stream
+// is still draining: it does whatever does not depend on earlier kernels (a matrix product starts
+// loading its weights), waits for the predecessor to have completed and flushed (`pdl_wait`), and only
+// then lets its own successor start (`pdl_launch_dependents`; a long kernel does so when its main
+// loop is done).  So at most one successor is resident and waiting at any time: letting successors
+// start earlier was measured to cost more (their waiting blocks take registers and warp slots from
+// the kernel that is running) than it gains.  Nothing is read from, or written to, memory that
+// another kernel of the step touches before the wait.  Launch latency and the ramp-up of the weight
+// stream thus overlap the previous kernel's tail.  PE_B200_PDL=0 switches the launch attribute off
+// (the two instructions are then no-ops).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("PE_B200_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 // ---- element conversion ----------------------------------------------------------------------

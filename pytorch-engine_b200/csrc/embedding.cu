@@ -7,6 +7,8 @@ namespace pe {
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int n_tokens, int hidden, int vocab, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x;
   if (row >= n_tokens) return;
   int id = ids[row];
@@ -29,9 +31,9 @@ extern "C" int pe_embed_gather(int dtype, const void* table, const int* ids, flo
   if (hidden <= 0 || vocab <= 0) return PE_ERR_BAD_ARGUMENT;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == PE_F32)
-    pe::embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, n_tokens, hidden, vocab, status);
+    pe::launch(pe::embed_gather_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, out, n_tokens, hidden, vocab, status);
   else if (dtype == PE_BF16)
-    pe::embed_gather_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, n_tokens, hidden, vocab, status);
+    pe::launch(pe::embed_gather_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, n_tokens, hidden, vocab, status);
   else
     return PE_ERR_UNSUPPORTED_DTYPE;
   PE_LAUNCH_CHECK();

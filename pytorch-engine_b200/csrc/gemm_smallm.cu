@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(WARPS * 32, NT == 1 ? 16 / WARPS : 1) gemm_sma
   struct Batch {
     uint4 wl[U], wh[U], vl[PAIR ? U : 1], vh[PAIR ? U : 1], xb[U][NT];
   };
-  auto load = [&](Batch& bt, int kb) {
+  auto load_w = [&](Batch& bt, int kb) {
     const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -106,9 +106,21 @@ __global__ void __launch_bounds__(WARPS * 32, NT == 1 ? 16 / WARPS : 1) gemm_sma
         bt.vl[u] = live ? ldg_stream(w2_lo + blk * 4) : zero;
         bt.vh[u] = live ? ldg_stream(w2_hi + blk * 4) : zero;
       }
+    }
+  };
+  auto load_x = [&](Batch& bt, int kb) {
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int blk = kb + u;
+      const bool live = blk < kb_hi && (blk * 4 + t) < k_chunks;
 #pragma unroll
       for (int n = 0; n < NT; ++n) bt.xb[u][n] = (live && x_ok[n]) ? ldg_cached(xr[n] + blk * 4) : zero;
     }
+  };
+  auto load = [&](Batch& bt, int kb) {
+    load_w(bt, kb);
+    load_x(bt, kb);
   };
   auto fold = [&](const Batch& bt) {
 #pragma unroll
@@ -124,14 +136,19 @@ __global__ void __launch_bounds__(WARPS * 32, NT == 1 ? 16 / WARPS : 1) gemm_sma
       }
     }
   };
+  // The weights do not depend on the kernels before this one: start the first batch of weight loads,
+  // and only then wait for the predecessor, whose output is the activations.
   Batch b0, b1;
-  load(b0, kb_lo);
+  load_w(b0, kb_lo);
+  pdl_wait();
+  load_x(b0, kb_lo);
   for (int kb = kb_lo; kb < kb_hi; kb += 2 * U) {
     load(b1, kb + U);
     fold(b0);
     load(b0, kb + 2 * U);
     fold(b1);
   }
+  pdl_launch_dependents();  // the stream of weights is done: the next kernel may start its own
   // sum the K slices in warp order
   if (WARPS > 1) {
 #pragma unroll
@@ -179,10 +196,10 @@ static int launch(const Args& a, cudaStream_t stream) {
   int warps = 1;
   while (warps < 8 && (long long)blocks * warps < want_warps && kblocks / (warps * 2) >= 2 * U) warps *= 2;
   switch (warps) {
-    case 1: gemm_smallm_kernel<NT, PAIR, 1, U, OutT><<<blocks, 32, 0, stream>>>(a); break;
-    case 2: gemm_smallm_kernel<NT, PAIR, 2, U, OutT><<<blocks, 64, 0, stream>>>(a); break;
-    case 4: gemm_smallm_kernel<NT, PAIR, 4, U, OutT><<<blocks, 128, 0, stream>>>(a); break;
-    default: gemm_smallm_kernel<NT, PAIR, 8, U, OutT><<<blocks, 256, 0, stream>>>(a); break;
+    case 1: pe::launch(gemm_smallm_kernel<NT, PAIR, 1, U, OutT>, blocks, 32, 0, stream, a); break;
+    case 2: pe::launch(gemm_smallm_kernel<NT, PAIR, 2, U, OutT>, blocks, 64, 0, stream, a); break;
+    case 4: pe::launch(gemm_smallm_kernel<NT, PAIR, 4, U, OutT>, blocks, 128, 0, stream, a); break;
+    default: pe::launch(gemm_smallm_kernel<NT, PAIR, 8, U, OutT>, blocks, 256, 0, stream, a); break;
   }
   PE_LAUNCH_CHECK();
   return PE_OK;

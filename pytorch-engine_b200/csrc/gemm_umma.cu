@@ -124,6 +124,8 @@ gemm_umma_kernel(Params p, const __grid_constant__ CUtensorMap amap, const __gri
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = tmem_holder;
+  pdl_wait();  // set-up (barriers, tensor memory) is done; now the inputs must be complete
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ---- producer ----
@@ -319,7 +321,7 @@ extern "C" int pe_gemm_umma(const void* x, long long ldx, const void* w, void* y
   }
   const int tiles = p.m_tiles * p.n_tiles;
   const int grid = tiles < n_sms ? tiles : n_sms;
-  gemm_umma_kernel<<<grid, kThreads, smem, stream>>>(p, amap, bmap);
+  pe::launch(gemm_umma_kernel, grid, kThreads, smem, stream, p, amap, bmap);
   PE_LAUNCH_CHECK();
   return PE_OK;
 }

@@ -19,6 +19,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ residual, const TDelta* __res
                                const int* __restrict__ rows, int n_rows, int dim, float eps) {
   extern __shared__ float row_buf[];  // dim floats
   __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x;
   if (r >= n_rows) return;
   const size_t src = rows ? (size_t)rows[r] : (size_t)r;
@@ -49,6 +51,8 @@ __global__ void rmsnorm_plain_kernel(const T* __restrict__ x, const float* __res
                                      int n_rows, int dim, float eps) {
   extern __shared__ float row_buf[];
   __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x;
   if (r >= n_rows) return;
   float ss = 0.f;
@@ -84,11 +88,11 @@ extern "C" int pe_rmsnorm_residual(int dtype, float* residual, const void* delta
   if (dtype == PE_F32) {
     auto k = pe::rmsnorm_kernel<float, float>;
     if ((e = pe::set_smem(k, smem))) return e;
-    k<<<n_rows, threads, smem, stream>>>(residual, (const float*)delta, weight, (float*)out, rows, n_rows, dim, eps);
+    pe::launch(k, n_rows, threads, smem, stream, residual, (const float*)delta, weight, (float*)out, rows, n_rows, dim, eps);
   } else if (dtype == PE_BF16) {
     auto k = pe::rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16>;
     if ((e = pe::set_smem(k, smem))) return e;
-    k<<<n_rows, threads, smem, stream>>>(residual, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows, n_rows, dim, eps);
+    pe::launch(k, n_rows, threads, smem, stream, residual, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows, n_rows, dim, eps);
   } else {
     return PE_ERR_UNSUPPORTED_DTYPE;
   }
@@ -107,11 +111,11 @@ extern "C" int pe_rmsnorm(int dtype, const void* x, const float* weight, void* o
   if (dtype == PE_F32) {
     auto k = pe::rmsnorm_plain_kernel<float>;
     if ((e = pe::set_smem(k, smem))) return e;
-    k<<<n_rows, threads, smem, stream>>>((const float*)x, weight, (float*)out, n_rows, dim, eps);
+    pe::launch(k, n_rows, threads, smem, stream, (const float*)x, weight, (float*)out, n_rows, dim, eps);
   } else if (dtype == PE_BF16) {
     auto k = pe::rmsnorm_plain_kernel<__nv_bfloat16>;
     if ((e = pe::set_smem(k, smem))) return e;
-    k<<<n_rows, threads, smem, stream>>>((const __nv_bfloat16*)x, weight, (__nv_bfloat16*)out, n_rows, dim, eps);
+    pe::launch(k, n_rows, threads, smem, stream, (const __nv_bfloat16*)x, weight, (__nv_bfloat16*)out, n_rows, dim, eps);
   } else {
     return PE_ERR_UNSUPPORTED_DTYPE;
   }

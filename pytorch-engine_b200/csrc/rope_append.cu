@@ -13,6 +13,8 @@ namespace pe {
 // token_seq[t] = index of the batch entry that token t belongs to; token_pos[t] = its position.
 __global__ void batch_expand_kernel(const int* __restrict__ seq_qstart, const int* __restrict__ seq_past,
                                     int n_seqs, int* __restrict__ token_seq, int* __restrict__ token_pos) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.x;
   if (b >= n_seqs) return;
   const int q0 = seq_qstart[b], q1 = seq_qstart[b + 1], past = seq_past[b];
@@ -46,6 +48,8 @@ struct RopeAppendArgs {
 
 template <typename T>
 __global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y * (blockDim.x >> 5) + warp;
@@ -151,7 +155,7 @@ __global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
 extern "C" int pe_batch_expand(const int* seq_qstart, const int* seq_past, int n_seqs, int* token_seq, int* token_pos,
                                cudaStream_t stream) {
   if (n_seqs <= 0) return PE_OK;
-  pe::batch_expand_kernel<<<n_seqs, 128, 0, stream>>>(seq_qstart, seq_past, n_seqs, token_seq, token_pos);
+  pe::launch(pe::batch_expand_kernel, n_seqs, 128, 0, stream, seq_qstart, seq_past, n_seqs, token_seq, token_pos);
   PE_LAUNCH_CHECK();
   return PE_OK;
 }
@@ -178,9 +182,9 @@ extern "C" int pe_qk_norm_rope_append(int dtype, void* qkv, long long ld, int n_
   dim3 grid(n_tokens, (total_heads + warps - 1) / warps);
   if (grid.y > 65535) return PE_ERR_UNSUPPORTED_SIZE;
   if (dtype == PE_F32)
-    pe::qk_norm_rope_append_kernel<float><<<grid, warps * 32, 0, stream>>>(a);
+    pe::launch(pe::qk_norm_rope_append_kernel<float>, grid, warps * 32, 0, stream, a);
   else if (dtype == PE_BF16)
-    pe::qk_norm_rope_append_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(a);
+    pe::launch(pe::qk_norm_rope_append_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream, a);
   else
     return PE_ERR_UNSUPPORTED_DTYPE;
   PE_LAUNCH_CHECK();

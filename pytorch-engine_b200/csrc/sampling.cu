@@ -96,6 +96,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleArgs a) {
   __shared__ float c_val[kMaxCompact];
   __shared__ int c_idx[kMaxCompact];
   __shared__ int scan[kSampleThreads];
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
   const float* src = a.logits + (size_t)row * a.ld;
@@ -237,6 +239,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleArgs a) {
 // logits[row, id] for the unique ids among recent[row, 0..count): negative -> * penalty, else / penalty.
 __global__ void repetition_penalty_kernel(float* logits, long long ld, int vocab, const int* recent, int recent_stride,
                                           const int* recent_count, float penalty) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int row = blockIdx.x;
   const int n = min(recent_count[row], recent_stride);
   const int* r = recent + (size_t)row * recent_stride;
@@ -267,7 +271,7 @@ extern "C" int pe_sample(const float* logits, long long ld, int n_rows, int voca
   a.logits = logits; a.ld = ld; a.n_rows = n_rows; a.vocab = vocab; a.temperature = temperature; a.top_k = top_k;
   a.top_p = top_p; a.min_p = min_p; a.seed = seed; a.row_request = row_request; a.row_step = row_step;
   a.out_tokens = out_tokens;
-  pe::sample_kernel<<<n_rows, pe::kSampleThreads, 0, stream>>>(a);
+  pe::launch(pe::sample_kernel, n_rows, pe::kSampleThreads, 0, stream, a);
   PE_LAUNCH_CHECK();
   return PE_OK;
 }
@@ -276,7 +280,7 @@ extern "C" int pe_repetition_penalty(float* logits, long long ld, int n_rows, in
                                      int recent_stride, const int* recent_count, float penalty, cudaStream_t stream) {
   if (n_rows <= 0 || penalty == 1.0f) return PE_OK;
   if (penalty <= 0.f) return PE_ERR_BAD_ARGUMENT;
-  pe::repetition_penalty_kernel<<<n_rows, 256, 0, stream>>>(logits, ld, vocab, recent, recent_stride, recent_count, penalty);
+  pe::launch(pe::repetition_penalty_kernel, n_rows, 256, 0, stream, logits, ld, vocab, recent, recent_stride, recent_count, penalty);
   PE_LAUNCH_CHECK();
   return PE_OK;
 }

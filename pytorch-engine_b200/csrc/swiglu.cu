@@ -9,6 +9,8 @@ namespace pe {
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_rows, int inter,
                                 size_t in_stride) {
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t total = (size_t)n_rows * inter;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / inter, c = i - r * inter;
@@ -29,9 +31,9 @@ extern "C" int pe_silu_mul(int dtype, const void* gate_up, void* out, int n_rows
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == PE_F32)
-    pe::silu_mul_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, n_rows, inter, (size_t)2 * inter);
+    pe::launch(pe::silu_mul_kernel<float>, (int)blocks, threads, 0, stream, (const float*)gate_up, (float*)out, n_rows, inter, (size_t)2 * inter);
   else if (dtype == PE_BF16)
-    pe::silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, n_rows, inter, (size_t)2 * inter);
+    pe::launch(pe::silu_mul_kernel<__nv_bfloat16>, (int)blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, n_rows, inter, (size_t)2 * inter);
   else
     return PE_ERR_UNSUPPORTED_DTYPE;
   PE_LAUNCH_CHECK();
