@@ -39,6 +39,36 @@ class BufferPool:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
 
 
+class PinnedStager:
+    """Host-to-device copies of small int32 arrays through a ring of pinned buffers.  A buffer is
+    reused only after the copy that last read it has finished (an event per buffer), so the host may
+    run ahead of the device by several steps."""
+
+    def __init__(self, device, capacity: int = 1 << 16, depth: int = 4) -> None:
+        self.device = torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self.capacity = capacity
+        self.bufs = [torch.empty(capacity, dtype=torch.int32, pin_memory=self.cuda) for _ in range(depth)]
+        self.events = [None] * depth
+        self.next = 0
+
+    def send(self, ints: Sequence[int], dst: torch.Tensor) -> None:
+        n = len(ints)
+        if n > self.capacity or not self.cuda:
+            dst.copy_(torch.tensor(ints, dtype=torch.int32))
+            return
+        i = self.next
+        self.next = (i + 1) % len(self.bufs)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.bufs[i][:n]
+        buf.copy_(torch.tensor(ints, dtype=torch.int32))
+        dst.copy_(buf, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self.events[i] = ev
+
+
 @dataclass
 class StepEntry:
     """One sequence's share of a step: its cache slot, its next tokens, and the indices among

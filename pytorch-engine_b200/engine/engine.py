@@ -44,6 +44,21 @@ def resolve_dtype(dtype: Union[str, torch.dtype]) -> torch.dtype:
     return _DTYPES[dtype]
 
 
+class _LoopBackend:
+    """What the generation loop drives.  A step is not followed by a read of the status word of its
+    own: the sampler's single device-to-host copy brings the tokens and the status word together."""
+
+    def __init__(self, engine: "Engine") -> None:
+        self.engine = engine
+        self.alloc_slot = engine.alloc_slot
+        self.free_slot = engine.free_slot
+        self.free_pages = engine.free_pages
+        self.sample = engine.sample
+
+    def step(self, entries):
+        return self.engine.runner.step(entries, check=False)
+
+
 class Engine:
     def __init__(self, model_path: Optional[str] = None, *, dtype: Union[str, torch.dtype] = "bfloat16",
                  max_context_len: Optional[int] = None, max_cache_tokens: Optional[int] = None, max_batch: int = 64,
@@ -86,8 +101,8 @@ class Engine:
         self.cache = PagedCache(self.model.cache_requests(), max_tokens=self.max_cache_tokens, max_slots=max_slots,
                                 max_seq_len=self.max_context_len, dtype=self.dtype, device=self.device)
         self.runner = ModelRunner(self.model, self.cache, cuda_graphs=enable_cuda_graph)
-        self.sampler = Sampler(self.device)
-        self.loop = GenerationLoop(self, max_context=self.max_context_len, max_batch=self.max_batch,
+        self.sampler = Sampler(self.device, self.runtime)
+        self.loop = GenerationLoop(_LoopBackend(self), max_context=self.max_context_len, max_batch=self.max_batch,
                                    eos_token_ids=config.stop_token_ids, bos_token_id=config.bos_token)
         self.load_time_s = time.perf_counter() - t0
         if verbose:

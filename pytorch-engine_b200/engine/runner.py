@@ -16,7 +16,7 @@ import torch
 
 from ..cache import PagedCache
 from ..kernels import ops
-from .batch import BufferPool, StepContext, StepEntry
+from .batch import BufferPool, PinnedStager, StepContext, StepEntry
 from .model import DecoderModel
 
 
@@ -35,6 +35,7 @@ class ModelRunner:
         self.cache = cache
         self.runtime = model.runtime
         self.pool = BufferPool(self.runtime.device)
+        self.stager = PinnedStager(self.runtime.device)
         self.cuda_graphs = bool(cuda_graphs) and self.runtime.is_cuda and model.graph_safe()
         self._graphs: Dict[int, _DecodeGraph] = {}
         self.steps_run = 0
@@ -70,13 +71,12 @@ class ModelRunner:
         n_seqs = len(entries)
         q_lens = [len(e.tokens) for e in entries]
         decode = all(q == 1 for q in q_lens)
-        host = torch.tensor(ints, dtype=torch.int32)
         if decode and self.cuda_graphs and n_want == n_seqs and all(tuple(e.want) == (0,) for e in entries):
-            logits = self._step_graph(host, n_seqs)
+            logits = self._step_graph(ints, n_seqs)
         else:
             ctx = StepContext(self.runtime, self.pool, n_tokens=n_tokens, n_seqs=n_seqs, max_q=max(q_lens),
                               decode=decode, max_kv_len=max(p + q for p, q in zip(pasts, q_lens)), n_want=n_want)
-            ctx.meta.copy_(host)
+            self.stager.send(ints, ctx.meta)
             ops.batch_expand(ctx.seq_qstart, ctx.seq_past, n_seqs, ctx.token_seq, ctx.token_pos)
             logits = self.model.forward(ctx, self.cache)
         for e, past in zip(entries, pasts):
@@ -86,12 +86,12 @@ class ModelRunner:
             self.runtime.raise_on_status()
         return logits
 
-    def _step_graph(self, host_meta: torch.Tensor, n_seqs: int) -> torch.Tensor:
+    def _step_graph(self, meta_ints, n_seqs: int) -> torch.Tensor:
         g = self._graphs.get(n_seqs)
         if g is None:
-            g = self._capture(host_meta, n_seqs)
+            g = self._capture(torch.tensor(meta_ints, dtype=torch.int32), n_seqs)
         else:
-            g.ctx.meta.copy_(host_meta)
+            self.stager.send(meta_ints, g.ctx.meta)
             g.graph.replay()
             ops.count_replay(g.launches)
         return g.logits

@@ -30,7 +30,13 @@ class Runtime:
             raise KernelError(f"run dtype must be float32 or bfloat16, got {dtype}")
         self.dtype = dtype
         self.is_cuda = self.device.type == "cuda"
-        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # the status word (4 ints) and, right behind it, room for the tokens a sampler draws: one
+        # device-to-host copy then brings both
+        self.max_result_rows = 8192
+        self._status_and_tokens = torch.zeros(4 + self.max_result_rows, dtype=torch.int32, device=self.device)
+        self.status = self._status_and_tokens[:4]
+        self.token_area = self._status_and_tokens[4:]
+        self._host_result = None
         self._adopted: Dict[Tuple[int, torch.dtype], torch.Tensor] = {}
         self.gemm_backend = None  # a callable (x, weight, out, out_dtype) -> tensor or None that takes over products
         self.own_small_gemm = True  # products with few rows run on csrc/gemm_smallm.cu
@@ -72,6 +78,23 @@ class Runtime:
         rows = 9 if pair_offset else self.large_gemm_rows   # the fused gate wins at every size above the small kernel's
         return (self.own_large_gemm and x.dim() == 2 and x.shape[0] >= rows
                 and ops.gemm_umma_supported(x, weight, pair_offset))
+
+    def fetch_tokens(self, n: int):
+        """The first ``n`` ints of ``token_area`` as a list, after checking the status word: one
+        device-to-host copy for both (the copy waits for the step's kernels)."""
+        if self._host_result is None:
+            self._host_result = torch.empty(4 + self.max_result_rows, dtype=torch.int32,
+                                            pin_memory=self.is_cuda)
+        host = self._host_result[:4 + n]
+        host.copy_(self._status_and_tokens[:4 + n], non_blocking=True)
+        if self.is_cuda:
+            torch.cuda.current_stream(self.device).synchronize()
+        vals = host.tolist()
+        if vals[0] != 0:
+            self.status.zero_()
+            msg = STATUS_MESSAGES.get(vals[0], "kernel status {0}").format(*vals[1:4])
+            raise KernelError(f"a kernel reported an error during the step: {msg}")
+        return vals[4:]
 
     # ---- matrix product ----------------------------------------------------------------------
     def linear(self, x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,

@@ -12,8 +12,12 @@ RECENT_WINDOW = 256  # the reference penalises the unique ids among the last 256
 
 
 class Sampler:
-    def __init__(self, device) -> None:
+    def __init__(self, device, runtime=None) -> None:
+        """With a ``runtime`` the drawn tokens land behind its status word and come back together with
+        it in one copy (``Runtime.fetch_tokens``), which also raises if a kernel reported an error."""
         self.device = torch.device(device)
+        self.runtime = runtime
+        self._stager = None
 
     def sample(self, logits: torch.Tensor, params: SamplingParams, seed: int, requests: Sequence[int],
                steps: Sequence[int], recent: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
@@ -33,6 +37,17 @@ class Sampler:
                 if tail:
                     rec[r, :len(tail)] = torch.tensor(tail, dtype=torch.int32)
             ops.repetition_penalty(logits, rec.to(self.device), cnt.to(self.device), params.repetition_penalty)
+        rt = self.runtime
+        if rt is not None and n <= rt.max_result_rows:
+            from ..engine.batch import PinnedStager
+            if self._stager is None:
+                self._stager = PinnedStager(self.device)
+                self._meta = torch.empty(2 * rt.max_result_rows, dtype=torch.int32, device=self.device)
+            meta = self._meta[:2 * n]
+            self._stager.send(list(requests) + list(steps), meta)
+            out = rt.token_area[:n]
+            ops.sample(logits, params.temperature, params.top_k, params.top_p, params.min_p, seed, meta[:n], meta[n:], out)
+            return rt.fetch_tokens(n)
         meta = torch.tensor([list(requests), list(steps)], dtype=torch.int32).to(self.device)
         out = torch.empty((n,), dtype=torch.int32, device=self.device)
         ops.sample(logits, params.temperature, params.top_k, params.top_p, params.min_p, seed, meta[0], meta[1], out)
