@@ -107,7 +107,7 @@ __device__ __forceinline__ char* align_1024(char* p) {
 // ---- prefill ---------------------------------------------------------------------------------------
 // grid: (row tiles of 64, n_kv_heads, n_seqs); block: 128 threads.
 template <int HD>
-__global__ void __launch_bounds__(128) prefill_kernel(Args a, const __grid_constant__ CUtensorMap kmap,
+__global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_constant__ CUtensorMap kmap,
                                                       const __grid_constant__ CUtensorMap vmap) {
   extern __shared__ char smem_raw[];
   __shared__ uint64_t bars[2];
@@ -117,14 +117,16 @@ __global__ void __launch_bounds__(128) prefill_kernel(Args a, const __grid_const
   constexpr int STAGE = 2 * BN * HD * 2;      // K and V tile
   constexpr int KS = HD / 16;                 // k-steps of Q.K^T
   constexpr int NO = HD / 8;                  // n-tiles of the output
-  char* q_s = smem + 2 * STAGE;               // [64][HD] swizzled
+  // Q is staged in the second K/V stage: its fragments are in registers before that stage is first filled
+  char* q_s = smem + STAGE;                   // [64][HD] swizzled
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int b = blockIdx.z, kvh = blockIdx.y;
   const int q0 = a.seq_qstart[b], q_len = a.seq_qstart[b + 1] - q0, past = a.seq_past[b];
   const int group = a.group;
   const int n_rows = q_len * group;
-  const int row0 = blockIdx.x * 64;
+  // late rows see the most keys: they go first, so that the longest blocks do not form the tail
+  const int row0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * 64;
   if (row0 >= n_rows) return;
   const int slot = a.seq_slot[b];
   const int last_row = min(n_rows, row0 + 64) - 1;
@@ -159,6 +161,7 @@ __global__ void __launch_bounds__(128) prefill_kernel(Args a, const __grid_const
     const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
     ldmatrix_x4(qf[ks], smem_u32(q_s) + tile_off<HD>(r, ks * 2 + (lane >> 4)));
   }
+  __syncthreads();  // every warp has its Q fragments: the stage that held Q may now be filled with keys
   // this thread's two rows
   const int r_lo = row0 + warp * 16 + g, r_hi = r_lo + 8;
   const int pos_lo = past + r_lo / group, pos_hi = past + r_hi / group;   // rows beyond n_rows are never stored
@@ -488,7 +491,7 @@ static int launch(const Args& a, bool decode, int n_seqs, int max_q, cudaStream_
   if (me == 0) me = tma::make_map_2d_bf16(&vmap, a.v_pages, HD, rows, HD, 64, BN);
   if (me != 0) return me < 0 ? me : PE_ERR_BAD_ARGUMENT;
   if (!decode) {
-    const size_t smem = 1024 + 2 * STAGE + 64 * HD * 2;
+    const size_t smem = 1024 + 2 * STAGE;
     auto k = prefill_kernel<HD>;
     int e = opt_in(k, smem);
     if (e) return e;
