@@ -44,6 +44,62 @@ __global__ void rmsnorm_kernel(float* __restrict__ residual, const TDelta* __res
   }
 }
 
+// The same with 4-element accesses (16-byte loads and stores of the float32 stream), for widths that
+// are a multiple of 4; rows then start on 16-byte boundaries.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+};
+
+template <typename TDelta, typename TOut>
+__global__ void rmsnorm_vec4_kernel(float* __restrict__ residual, const TDelta* __restrict__ delta,
+                                    const float* __restrict__ weight, TOut* __restrict__ out,
+                                    const int* __restrict__ rows, int n_rows, int dim, float eps) {
+  extern __shared__ float row_buf[];  // dim floats
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  if (r >= n_rows) return;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  float* res_row = residual + src * dim;
+  const TDelta* d_row = delta ? delta + src * dim : nullptr;
+  const bool write_back = (d_row != nullptr) && (rows == nullptr);
+  float ss = 0.f;
+  for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) {
+    float4 h = Vec4<float>::load(res_row + c);
+    if (d_row) {
+      const float4 d = Vec4<TDelta>::load(d_row + c);
+      h.x += d.x; h.y += d.y; h.z += d.z; h.w += d.w;
+      if (write_back) Vec4<float>::store(res_row + c, h);
+    }
+    *reinterpret_cast<float4*>(row_buf + c) = h;
+    ss += h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)dim + eps);
+  TOut* o_row = out + (size_t)r * dim;
+  for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) {
+    const float4 h = *reinterpret_cast<const float4*>(row_buf + c);
+    const float4 w = Vec4<float>::load(weight + c);
+    Vec4<TOut>::store(o_row + c, make_float4(h.x * inv * w.x, h.y * inv * w.y, h.z * inv * w.z, h.w * inv * w.w));
+  }
+}
+
 // Plain RMSNorm of a tensor in the run dtype (rows of any width), used by parts that normalise
 // something other than the residual stream.
 template <typename T>
@@ -85,12 +141,14 @@ extern "C" int pe_rmsnorm_residual(int dtype, float* residual, const void* delta
   if (smem > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;  // rows wider than 51,200 features
   const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
   int e;
+  const bool vec = (dim % 4 == 0) && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
+                   ((uintptr_t)out % 16 == 0) && ((uintptr_t)delta % 16 == 0);
   if (dtype == PE_F32) {
-    auto k = pe::rmsnorm_kernel<float, float>;
+    auto k = vec ? pe::rmsnorm_vec4_kernel<float, float> : pe::rmsnorm_kernel<float, float>;
     if ((e = pe::set_smem(k, smem))) return e;
     pe::launch(k, n_rows, threads, smem, stream, residual, (const float*)delta, weight, (float*)out, rows, n_rows, dim, eps);
   } else if (dtype == PE_BF16) {
-    auto k = pe::rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16>;
+    auto k = vec ? pe::rmsnorm_vec4_kernel<__nv_bfloat16, __nv_bfloat16> : pe::rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16>;
     if ((e = pe::set_smem(k, smem))) return e;
     pe::launch(k, n_rows, threads, smem, stream, residual, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, rows, n_rows, dim, eps);
   } else {

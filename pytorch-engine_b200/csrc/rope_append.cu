@@ -46,7 +46,20 @@ struct RopeAppendArgs {
   int* status;
 };
 
-template <typename T>
+template <typename T> __device__ __forceinline__ float2 load2(const T* p);
+template <> __device__ __forceinline__ float2 load2<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <> __device__ __forceinline__ float2 load2<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+template <typename T> __device__ __forceinline__ void store2(T* p, float2 v);
+template <> __device__ __forceinline__ void store2<float>(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+template <> __device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16* p, float2 v) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y);
+}
+
+// PAIRS: every access covers two adjacent features (head size and half the rotary size even, rows
+// aligned to two elements); otherwise one feature at a time.
+template <typename T, bool PAIRS>
 __global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
   pdl_wait();
   pdl_launch_dependents();
@@ -98,8 +111,13 @@ __global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
   }
 
   if (!is_q && !is_k) {  // v: copy only
-    if (cache_row)
-      for (int c = lane; c < d; c += 32) cache_row[c] = row[c];
+    if (cache_row) {
+      if (PAIRS) {
+        for (int c = lane * 2; c < d; c += 64) store2<T>(cache_row + c, load2<T>(row + c));
+      } else {
+        for (int c = lane; c < d; c += 32) cache_row[c] = row[c];
+      }
+    }
     return;
   }
 
@@ -107,9 +125,16 @@ __global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
   float inv = 1.f;
   if (w) {
     float ss = 0.f;
-    for (int c = lane; c < d; c += 32) {
-      const float x = to_f32<T>(row[c]);
-      ss += x * x;
+    if (PAIRS) {
+      for (int c = lane * 2; c < d; c += 64) {
+        const float2 x = load2<T>(row + c);
+        ss += x.x * x.x + x.y * x.y;
+      }
+    } else {
+      for (int c = lane; c < d; c += 32) {
+        const float x = to_f32<T>(row[c]);
+        ss += x * x;
+      }
     }
     ss = warp_sum(ss);
     inv = rsqrtf(ss / (float)d + a.eps);
@@ -129,6 +154,34 @@ __global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
   }
   const float* cs = a.cos_table ? a.cos_table + (size_t)pos * half : nullptr;
   const float* sn = a.sin_table ? a.sin_table + (size_t)pos * half : nullptr;
+  if (PAIRS) {
+    for (int j = lane * 2; j < half; j += 64) {
+      float2 x1 = load2<T>(row + j), x2 = load2<T>(row + j + half);
+      if (w) {
+        const float2 w1 = *reinterpret_cast<const float2*>(w + j), w2 = *reinterpret_cast<const float2*>(w + j + half);
+        x1.x *= inv * w1.x; x1.y *= inv * w1.y; x2.x *= inv * w2.x; x2.y *= inv * w2.y;
+      }
+      const float2 c = *reinterpret_cast<const float2*>(cs + j), sv = *reinterpret_cast<const float2*>(sn + j);
+      const float2 o1 = make_float2(x1.x * c.x - x2.x * sv.x, x1.y * c.y - x2.y * sv.y);
+      const float2 o2 = make_float2(x2.x * c.x + x1.x * sv.x, x2.y * c.y + x1.y * sv.y);
+      store2<T>(row + j, o1);
+      store2<T>(row + j + half, o2);
+      if (cache_row) {
+        store2<T>(cache_row + j, o1);
+        store2<T>(cache_row + j + half, o2);
+      }
+    }
+    for (int c = rot + lane * 2; c < d; c += 64) {
+      float2 x = load2<T>(row + c);
+      if (w) {
+        const float2 wv = *reinterpret_cast<const float2*>(w + c);
+        x.x *= inv * wv.x; x.y *= inv * wv.y;
+      }
+      store2<T>(row + c, x);
+      if (cache_row) store2<T>(cache_row + c, x);
+    }
+    return;
+  }
   // rotated pairs (j, j + half): both are read before either is written
   for (int j = lane; j < half; j += 32) {
     const float x1 = normed(j), x2 = normed(j + half);
@@ -181,11 +234,19 @@ extern "C" int pe_qk_norm_rope_append(int dtype, void* qkv, long long ld, int n_
   const int total_heads = n_heads + 2 * n_kv_heads;
   dim3 grid(n_tokens, (total_heads + warps - 1) / warps);
   if (grid.y > 65535) return PE_ERR_UNSUPPORTED_SIZE;
-  if (dtype == PE_F32)
-    pe::launch(pe::qk_norm_rope_append_kernel<float>, grid, warps * 32, 0, stream, a);
-  else if (dtype == PE_BF16)
-    pe::launch(pe::qk_norm_rope_append_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream, a);
-  else
+  // two features per access where everything is even and aligned (the usual case)
+  const size_t esz = dtype == PE_F32 ? 4 : 2;
+  const bool pairs = (head_dim % 2 == 0) && (rotary_dim % 4 == 0) && (ld % 2 == 0) && ((uintptr_t)qkv % (2 * esz) == 0) &&
+                     ((uintptr_t)k_pages % (2 * esz) == 0) && ((uintptr_t)v_pages % (2 * esz) == 0) &&
+                     ((uintptr_t)cos_table % 8 == 0) && ((uintptr_t)sin_table % 8 == 0) &&
+                     ((uintptr_t)q_norm_w % 8 == 0) && ((uintptr_t)k_norm_w % 8 == 0);
+  if (dtype == PE_F32) {
+    if (pairs) pe::launch(pe::qk_norm_rope_append_kernel<float, true>, grid, warps * 32, 0, stream, a);
+    else pe::launch(pe::qk_norm_rope_append_kernel<float, false>, grid, warps * 32, 0, stream, a);
+  } else if (dtype == PE_BF16) {
+    if (pairs) pe::launch(pe::qk_norm_rope_append_kernel<__nv_bfloat16, true>, grid, warps * 32, 0, stream, a);
+    else pe::launch(pe::qk_norm_rope_append_kernel<__nv_bfloat16, false>, grid, warps * 32, 0, stream, a);
+  } else
     return PE_ERR_UNSUPPORTED_DTYPE;
   PE_LAUNCH_CHECK();
   return PE_OK;

@@ -207,6 +207,41 @@ def test_long_decoding_and_first_tokens(pe, engines, oracles, tmp_path, key, dty
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("key", ["B", "D"])
+def test_random_cuts_into_steps(pe, engines, oracles, tmp_path, key, dtype):
+    """Three requests run together; every step brings each of them a random number of its next tokens
+    (one, a few, or many; a request that has none left sits the step out).  Whatever the cuts, the
+    logits at every position are those of the whole sequence."""
+    import random
+    cfg, w = oracles[key, dtype]
+    eng = engines(key, dtype)
+    for seed in range(3):
+        rng = random.Random(100 + seed)
+        seqs = {str(i): _tokens(cfg["vocab_size"], rng.choice([40, 97, 130, 201]), 200 + 10 * seed + i) for i in range(3)}
+        fed = {i: 0 for i in seqs}
+        rp = Replay(pe, eng, tmp_path)
+        while any(fed[i] < len(seqs[i]) for i in seqs):
+            entries, end = [], []
+            for i, toks in seqs.items():
+                left = len(toks) - fed[i]
+                if left == 0:
+                    continue
+                n = min(left, rng.choice([1, 1, 2, 5, 17, 64, 65, 120]))
+                entries.append((i, toks[fed[i]:fed[i] + n], list(range(n))))
+                fed[i] += n
+                if fed[i] == len(toks):
+                    end.append(i)
+            rp.run(entries, end=end)
+        want = {}
+        for i, toks in seqs.items():
+            ref = _ref(cfg, w, toks, dtype)
+            want.update({(i, j): ref[j] for j in range(len(toks))})
+        _check(rp.got, want, dtype, f"{key} random cuts, seed {seed}")
+    assert not eng.cache.live_slots
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_graph_replay_equals_eager_steps(pe, engines, oracles, tmp_path, dtype):
     cfg, w = oracles["B", dtype]
     toks = [_tokens(cfg["vocab_size"], 90, 40 + i) for i in range(3)]
