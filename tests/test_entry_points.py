@@ -1,0 +1,93 @@
+"""Command line, entry point and replay program without a GPU: options, errors, and the refusal
+to run without CUDA (there is no CPU fallback)."""
+import io
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from conftest import ROOT, TEST_CONFIGS
+
+
+def test_cli_options_follow_the_reference(pe):
+    from importlib import import_module
+    cli = import_module("pytorch-engine_b200.cli")
+    args = cli.build_parser().parse_args(["--model", "m", "--prompt-ids", "1,2,3", "--prompt-ids", "4 5"])
+    # defaults of the reference's SamplingConfig and of its --ctx / --no-cuda-graph flags
+    assert (args.max_tokens, args.temperature, args.top_k, args.top_p, args.min_p, args.repetition_penalty) == \
+        (512, 0.7, 40, 0.95, 0.05, 1.0)
+    assert args.ctx is None and args.no_cuda_graph is False and args.dtype == "bf16"
+    assert [cli._ids(t) for t in args.prompt_ids] == [[1, 2, 3], [4, 5]]
+
+
+def test_cli_needs_exactly_one_model_source(pe, capsys):
+    from importlib import import_module
+    cli = import_module("pytorch-engine_b200.cli")
+    assert cli.main(["--prompt-ids", "1"]) == 2
+    assert cli.main(["--model", "x", "--random", "tiny_a", "--prompt-ids", "1"]) == 2
+    assert "exactly one" in capsys.readouterr().err
+    assert cli.main(["--list-presets"]) == 0
+    assert "qwen3_8b" in capsys.readouterr().out
+
+
+def test_cli_writes_a_random_model(pe, tmp_path):
+    from importlib import import_module
+    cli = import_module("pytorch-engine_b200.cli")
+    assert cli.main(["--random", "tiny_a", "--seed", "4", "--write-random", str(tmp_path / "m")]) == 0
+    assert sorted(os.listdir(tmp_path / "m")) == ["config.json", "model.safetensors"]
+    assert pe.load_config(str(tmp_path / "m")) == pe.preset("tiny_a")
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the refusal on a machine without CUDA")
+def test_no_cuda_no_engine(pe, tmp_path):
+    cfg = pe.Qwen3Config.from_dict(TEST_CONFIGS["A"])
+    pe.write_random_model(str(tmp_path), cfg, 0)
+    with pytest.raises(pe.kernels.KernelError, match="no CPU path"):
+        pe.Engine(str(tmp_path))
+    with pytest.raises(pe.kernels.KernelError):
+        pe.kernels.ops.silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))
+
+
+def test_trace_run_rejects_bad_arguments():
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", "nowhere"],
+                          capture_output=True, text=True, timeout=120)
+    assert proc.returncode != 0 and "--out" in proc.stderr
+
+
+def test_replayer_bookkeeping_with_a_scripted_engine(pe, tmp_path):
+    """The replayer gives a slot at a request's first appearance, returns it at ``end``, writes a file
+    only when something is wanted, and refuses to end what is not live."""
+
+    class FakeEngine:
+        def __init__(self):
+            self.next, self.freed, self.calls = 0, [], []
+
+        def alloc_slot(self):
+            self.next += 1
+            return self.next - 1
+
+        def free_slot(self, s):
+            self.freed.append(s)
+
+        def step(self, entries):
+            self.calls.append([(e.slot, list(e.tokens), tuple(e.want)) for e in entries])
+            n = sum(len(e.want) for e in entries)
+            return torch.arange(n * 3, dtype=torch.float32).view(n, 3)
+
+    eng = FakeEngine()
+    rp = pe.engine.TraceReplayer(eng, str(tmp_path))
+    out = io.StringIO()
+    lines = [json.dumps({"step": 0, "entries": [{"id": "a", "tokens": [1, 2], "want": [1]}, {"id": "b", "tokens": [3], "want": []}], "end": []}),
+             "", json.dumps({"step": 1, "entries": [{"id": "a", "tokens": [4], "want": []}, {"id": "b", "tokens": [5], "want": []}], "end": ["a"]}),
+             json.dumps({"step": 5, "entries": [{"id": "c", "tokens": [6], "want": [0]}], "end": ["b", "c"]})]
+    assert rp.run(io.StringIO("\n".join(lines) + "\n"), out) == 0
+    assert out.getvalue().split() == ["done", "0", "done", "1", "done", "5"]
+    assert sorted(os.listdir(tmp_path)) == ["0.f32", "5.f32"]
+    assert eng.calls[0] == [(0, [1, 2], (1,)), (1, [3], ())] and eng.calls[2] == [(2, [6], (0,))]
+    assert eng.freed == [0, 1, 2] and rp.slots == {}
+    assert os.path.getsize(tmp_path / "0.f32") == 12
+    with pytest.raises(pe.engine.replay.TraceError):
+        rp.run_step({"step": 6, "entries": [], "end": ["zz"]})
