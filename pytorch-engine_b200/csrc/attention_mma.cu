@@ -60,6 +60,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the hardware approximation (one instruction, about 2 ulp; exp2(-inf) = 0): the result is
+// rounded to bfloat16 or summed into a float32 denominator, so this is within the path's precision.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -201,17 +208,31 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
       }
       // scale, mask, running max
       float mx_lo = -INFINITY, mx_hi = -INFINITY;
+      // a page that lies wholly in the past of every row of this warp (and inside every window) needs no mask
+      const bool full = (k0 + BN - 1 <= warp_first_pos) && (a.window <= 0 || k0 > warp_last_pos - a.window);
+      if (full) {
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
+        for (int n = 0; n < 8; ++n) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int kpos = k0 + n * 8 + 2 * t + (e & 1);
-          const int qpos = (e < 2) ? pos_lo : pos_hi;
-          bool vis = kpos <= qpos;
-          if (a.window > 0) vis = vis && (kpos > qpos - a.window);
-          const float v = vis ? s[n][e] * a.scale_log2 : -INFINITY;
-          s[n][e] = v;
-          if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+          for (int e = 0; e < 4; ++e) {
+            const float v = s[n][e] * a.scale_log2;
+            s[n][e] = v;
+            if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int kpos = k0 + n * 8 + 2 * t + (e & 1);
+            const int qpos = (e < 2) ? pos_lo : pos_hi;
+            bool vis = kpos <= qpos;
+            if (a.window > 0) vis = vis && (kpos > qpos - a.window);
+            const float v = vis ? s[n][e] * a.scale_log2 : -INFINITY;
+            s[n][e] = v;
+            if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+          }
         }
       }
       mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
@@ -219,15 +240,15 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
       const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-      const float al_lo = (m_lo == -INFINITY) ? 0.f : exp2f(m_lo - mn_lo);
-      const float al_hi = (m_hi == -INFINITY) ? 0.f : exp2f(m_hi - mn_hi);
+      const float al_lo = (m_lo == -INFINITY) ? 0.f : fast_exp2(m_lo - mn_lo);
+      const float al_hi = (m_hi == -INFINITY) ? 0.f : fast_exp2(m_hi - mn_hi);
       const float base_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, base_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
       float sum_lo = 0.f, sum_hi = 0.f;
       uint32_t pf[4][4];  // P as A operand: 4 k-steps of 16 keys
 #pragma unroll
       for (int n = 0; n < 8; ++n) {
-        const float p0 = exp2f(s[n][0] - base_lo), p1 = exp2f(s[n][1] - base_lo);
-        const float p2 = exp2f(s[n][2] - base_hi), p3 = exp2f(s[n][3] - base_hi);
+        const float p0 = fast_exp2(s[n][0] - base_lo), p1 = fast_exp2(s[n][1] - base_lo);
+        const float p2 = fast_exp2(s[n][2] - base_hi), p3 = fast_exp2(s[n][3] - base_hi);
         sum_lo += p0 + p1;
         sum_hi += p2 + p3;
         pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
@@ -369,13 +390,13 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
       const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-      const float al_lo = (m_lo == -INFINITY) ? 0.f : exp2f(m_lo - mn_lo);
-      const float al_hi = (m_hi == -INFINITY) ? 0.f : exp2f(m_hi - mn_hi);
+      const float al_lo = (m_lo == -INFINITY) ? 0.f : fast_exp2(m_lo - mn_lo);
+      const float al_hi = (m_hi == -INFINITY) ? 0.f : fast_exp2(m_hi - mn_hi);
       const float base_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, base_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
-      const float p00 = exp2f(s[0][0] - base_lo), p01 = exp2f(s[0][1] - base_lo);
-      const float p02 = exp2f(s[0][2] - base_hi), p03 = exp2f(s[0][3] - base_hi);
-      const float p10 = exp2f(s[1][0] - base_lo), p11 = exp2f(s[1][1] - base_lo);
-      const float p12 = exp2f(s[1][2] - base_hi), p13 = exp2f(s[1][3] - base_hi);
+      const float p00 = fast_exp2(s[0][0] - base_lo), p01 = fast_exp2(s[0][1] - base_lo);
+      const float p02 = fast_exp2(s[0][2] - base_hi), p03 = fast_exp2(s[0][3] - base_hi);
+      const float p10 = fast_exp2(s[1][0] - base_lo), p11 = fast_exp2(s[1][1] - base_lo);
+      const float p12 = fast_exp2(s[1][2] - base_hi), p13 = fast_exp2(s[1][3] - base_hi);
       float sum_lo = p00 + p01 + p10 + p11, sum_hi = p02 + p03 + p12 + p13;
       sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
       sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
@@ -428,7 +449,7 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
         const float mw = ml[(w * 16 + r) * 2];
-        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
+        const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - mm);
         ll += ml[(w * 16 + r) * 2 + 1] * f;
         aa += acc[(size_t)(w * 16 + r) * HD + c] * f;
       }

@@ -126,10 +126,18 @@ class Runtime:
             finally:
                 if prev:
                     torch.backends.cuda.matmul.allow_tf32 = True
-        if out_dtype is not None and out_dtype != x.dtype:
-            y = torch.mm(x, weight.t(), out_dtype=out_dtype)
-            if out is not None:
-                out.copy_(y)
-                return out
-            return y
-        return torch.mm(x, weight.t(), out=out) if out is not None else torch.mm(x, weight.t())
+        # library product in bfloat16: keep its reductions in float32
+        prev = torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction
+        if prev:
+            torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+        try:
+            if out_dtype is not None and out_dtype != x.dtype:
+                y = torch.mm(x, weight.t(), out_dtype=out_dtype)
+                if out is not None:
+                    out.copy_(y)
+                    return out
+                return y
+            return torch.mm(x, weight.t(), out=out) if out is not None else torch.mm(x, weight.t())
+        finally:
+            if prev:
+                torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = True
