@@ -296,6 +296,77 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
   }
 }
 
+// One warp folds its 16 keys (key0 .. key0+15 of the page that starts at position k0) into the
+// running softmax state of the group's rows.  Keys outside [k_first, k_hi) are masked.
+template <int HD>
+__device__ __forceinline__ void decode_fold_page(uint32_t ks_base, uint32_t vs_base, int key0, int k0, int k_first,
+                                                 int k_hi, float scale_log2, const uint32_t (&qf)[HD / 16][4],
+                                                 float (&o)[HD / 8][4], float& m_lo, float& m_hi, float& l_lo,
+                                                 float& l_hi, int lane) {
+  constexpr int KS = HD / 16;
+  constexpr int NO = HD / 8;
+  const int t = lane & 3;
+    if (k0 + key0 < k_hi && k0 + key0 + 15 >= k_first) {
+  float s[2][4];
+  s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    uint32_t kb[4];
+    const int key = key0 + (lane & 7) + (lane >> 4) * 8;
+    ldmatrix_x4(kb, ks_base + tile_off<HD>(key, ks * 2 + ((lane >> 3) & 1)));
+    mma_bf16(s[0], qf[ks], kb[0], kb[1]);
+    mma_bf16(s[1], qf[ks], kb[2], kb[3]);
+  }
+  float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int kpos = k0 + key0 + n * 8 + 2 * t + (e & 1);
+      const bool vis = kpos >= k_first && kpos < k_hi;
+      const float v = vis ? s[n][e] * scale_log2 : -INFINITY;
+      s[n][e] = v;
+      if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+    }
+  }
+  mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+  mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+  mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+  mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+  const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+  const float al_lo = (m_lo == -INFINITY) ? 0.f : fast_exp2(m_lo - mn_lo);
+  const float al_hi = (m_hi == -INFINITY) ? 0.f : fast_exp2(m_hi - mn_hi);
+  const float base_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, base_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
+  const float p00 = fast_exp2(s[0][0] - base_lo), p01 = fast_exp2(s[0][1] - base_lo);
+  const float p02 = fast_exp2(s[0][2] - base_hi), p03 = fast_exp2(s[0][3] - base_hi);
+  const float p10 = fast_exp2(s[1][0] - base_lo), p11 = fast_exp2(s[1][1] - base_lo);
+  const float p12 = fast_exp2(s[1][2] - base_hi), p13 = fast_exp2(s[1][3] - base_hi);
+  float sum_lo = p00 + p01 + p10 + p11, sum_hi = p02 + p03 + p12 + p13;
+  sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
+  sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
+  sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
+  sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+  l_lo = l_lo * al_lo + sum_lo;
+  l_hi = l_hi * al_hi + sum_hi;
+  m_lo = mn_lo;
+  m_hi = mn_hi;
+  uint32_t pf[4];
+  pf[0] = pack_bf16(p00, p01); pf[1] = pack_bf16(p02, p03); pf[2] = pack_bf16(p10, p11); pf[3] = pack_bf16(p12, p13);
+#pragma unroll
+  for (int n = 0; n < NO; ++n) {
+    o[n][0] *= al_lo; o[n][1] *= al_lo; o[n][2] *= al_hi; o[n][3] *= al_hi;
+  }
+#pragma unroll
+  for (int np = 0; np < NO / 2; ++np) {
+    uint32_t vb[4];
+    const int key = key0 + (lane & 7) + ((lane >> 3) & 1) * 8;
+    ldmatrix_x4_trans(vb, vs_base + tile_off<HD>(key, np * 2 + (lane >> 4)));
+    mma_bf16(o[np * 2], pf, vb[0], vb[1]);
+    mma_bf16(o[np * 2 + 1], pf, vb[2], vb[3]);
+  }
+}
+}
+
 // ---- decode ------------------------------------------------------------------------------------------
 // grid: (max_splits, n_kv_heads, n_seqs); block: 128 threads; STAGES pages in flight.
 template <int HD, int STAGES>
@@ -303,7 +374,9 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
                                                            const __grid_constant__ CUtensorMap vmap) {
   extern __shared__ char smem_raw[];
   __shared__ uint64_t bars[STAGES];
-  pdl_wait();
+  // The batch description and every page but the sequence's last were written before the kernel that
+  // precedes this one started, so they may be read before the dependency wait; the last page (it gets
+  // this step's key) and the queries come from that kernel and are read after it.
   char* smem = align_1024(smem_raw);
   constexpr int STAGE = 2 * BN * HD * 2;
   constexpr int KS = HD / 16;
@@ -323,13 +396,22 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
   const int k_first = max(k_lo, win_lo);         // first visible key of this range
   const int k_begin = k_first / BN * BN;
   const int n_tiles = (k_hi - k_begin + BN - 1) / BN;
+  const int last_page_k0 = (len - 1) / BN * BN;
   if (tid == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) tma::mbar_init(&bars[s], 1);
     tma::fence_barrier_init();
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s)
-      if (s < n_tiles) issue_page<HD>(a, &kmap, &vmap, slot, kvh, k_begin + s * BN, smem + s * STAGE, &bars[s]);
+      if (s < n_tiles && k_begin + s * BN != last_page_k0)
+        issue_page<HD>(a, &kmap, &vmap, slot, kvh, k_begin + s * BN, smem + s * STAGE, &bars[s]);
+  }
+  pdl_wait();
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s)
+      if (s < n_tiles && k_begin + s * BN == last_page_k0)
+        issue_page<HD>(a, &kmap, &vmap, slot, kvh, k_begin + s * BN, smem + s * STAGE, &bars[s]);
   }
   constexpr int CPR = HD / 8;
   for (int i = tid; i < 16 * CPR; i += 128) {
@@ -360,67 +442,8 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
       return;
     }
     const int k0 = k_begin + it * BN;
-    const int key0 = warp * 16;                  // this warp's 16 keys of the page
-    if (k0 + key0 < k_hi && k0 + key0 + 15 >= k_first) {
-      const uint32_t ks_base = smem_u32(smem + (it % STAGES) * STAGE), vs_base = ks_base + BN * HD * 2;
-      float s[2][4];
-      s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
-#pragma unroll
-      for (int ks = 0; ks < KS; ++ks) {
-        uint32_t kb[4];
-        const int key = key0 + (lane & 7) + (lane >> 4) * 8;
-        ldmatrix_x4(kb, ks_base + tile_off<HD>(key, ks * 2 + ((lane >> 3) & 1)));
-        mma_bf16(s[0], qf[ks], kb[0], kb[1]);
-        mma_bf16(s[1], qf[ks], kb[2], kb[3]);
-      }
-      float mx_lo = -INFINITY, mx_hi = -INFINITY;
-#pragma unroll
-      for (int n = 0; n < 2; ++n) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int kpos = k0 + key0 + n * 8 + 2 * t + (e & 1);
-          const bool vis = kpos >= k_first && kpos < k_hi;
-          const float v = vis ? s[n][e] * a.scale_log2 : -INFINITY;
-          s[n][e] = v;
-          if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
-        }
-      }
-      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-      const float al_lo = (m_lo == -INFINITY) ? 0.f : fast_exp2(m_lo - mn_lo);
-      const float al_hi = (m_hi == -INFINITY) ? 0.f : fast_exp2(m_hi - mn_hi);
-      const float base_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, base_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
-      const float p00 = fast_exp2(s[0][0] - base_lo), p01 = fast_exp2(s[0][1] - base_lo);
-      const float p02 = fast_exp2(s[0][2] - base_hi), p03 = fast_exp2(s[0][3] - base_hi);
-      const float p10 = fast_exp2(s[1][0] - base_lo), p11 = fast_exp2(s[1][1] - base_lo);
-      const float p12 = fast_exp2(s[1][2] - base_hi), p13 = fast_exp2(s[1][3] - base_hi);
-      float sum_lo = p00 + p01 + p10 + p11, sum_hi = p02 + p03 + p12 + p13;
-      sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
-      sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
-      sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
-      sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
-      l_lo = l_lo * al_lo + sum_lo;
-      l_hi = l_hi * al_hi + sum_hi;
-      m_lo = mn_lo;
-      m_hi = mn_hi;
-      uint32_t pf[4];
-      pf[0] = pack_bf16(p00, p01); pf[1] = pack_bf16(p02, p03); pf[2] = pack_bf16(p10, p11); pf[3] = pack_bf16(p12, p13);
-#pragma unroll
-      for (int n = 0; n < NO; ++n) {
-        o[n][0] *= al_lo; o[n][1] *= al_lo; o[n][2] *= al_hi; o[n][3] *= al_hi;
-      }
-#pragma unroll
-      for (int np = 0; np < NO / 2; ++np) {
-        uint32_t vb[4];
-        const int key = key0 + (lane & 7) + ((lane >> 3) & 1) * 8;
-        ldmatrix_x4_trans(vb, vs_base + tile_off<HD>(key, np * 2 + (lane >> 4)));
-        mma_bf16(o[np * 2], pf, vb[0], vb[1]);
-        mma_bf16(o[np * 2 + 1], pf, vb[2], vb[3]);
-      }
-    }
+    decode_fold_page<HD>(smem_u32(smem + (it % STAGES) * STAGE), smem_u32(smem + (it % STAGES) * STAGE) + BN * HD * 2,
+                         warp * 16, k0, k_first, k_hi, a.scale_log2, qf, o, m_lo, m_hi, l_lo, l_hi, lane);
     __syncthreads();
   }
   pdl_launch_dependents();
