@@ -49,7 +49,9 @@ class PinnedStager:
         self.cuda = self.device.type == "cuda"
         self.capacity = capacity
         self.bufs = [torch.empty(capacity, dtype=torch.int32, pin_memory=self.cuda) for _ in range(depth)]
-        self.events = [None] * depth
+        self.views = [b.numpy() for b in self.bufs]      # the same memory, for fast filling from lists
+        self.events = [torch.cuda.Event() if self.cuda else None for _ in range(depth)]
+        self.used = [False] * depth
         self.next = 0
 
     def send(self, ints: Sequence[int], dst: torch.Tensor) -> None:
@@ -59,14 +61,12 @@ class PinnedStager:
             return
         i = self.next
         self.next = (i + 1) % len(self.bufs)
-        if self.events[i] is not None:
+        if self.used[i]:
             self.events[i].synchronize()
-        buf = self.bufs[i][:n]
-        buf.copy_(torch.tensor(ints, dtype=torch.int32))
-        dst.copy_(buf, non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record(torch.cuda.current_stream(self.device))
-        self.events[i] = ev
+        self.views[i][:n] = ints
+        dst.copy_(self.bufs[i][:n], non_blocking=True)
+        self.events[i].record()
+        self.used[i] = True
 
 
 @dataclass
