@@ -91,6 +91,16 @@ def test_silu_mul(ops, dtype, n, inter):
     assert rel_err(out.float().cpu(), want) < KTOL[dtype]
 
 
+def test_batch_expand(ops):
+    qstart = torch.tensor([0, 3, 4, 4, 9], dtype=torch.int32, device=DEV)      # the third sequence brings nothing
+    past = torch.tensor([10, 0, 7, 100], dtype=torch.int32, device=DEV)
+    seq = torch.full((9,), -1, dtype=torch.int32, device=DEV)
+    pos = torch.full((9,), -1, dtype=torch.int32, device=DEV)
+    ops.batch_expand(qstart, past, 4, seq, pos)
+    assert seq.tolist() == [0, 0, 0, 1, 3, 3, 3, 3, 3]
+    assert pos.tolist() == [10, 11, 12, 0, 100, 101, 102, 103, 104]
+
+
 class PagedSetup:
     """A batch of sequences with keys and values scattered over shuffled pages of a pool."""
 

@@ -129,6 +129,40 @@ def test_swiglu_embedding_and_head_parts(pe, dtype):
     assert rel_err(logits.cpu(), x[:4].float() @ table.float().T) < PTOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_block_arrangement_alone(pe, dtype):
+    """The pre-norm arrangement around real parts: one block of test configuration B, a whole prompt,
+    against the plain block.  The block hands its last delta on instead of adding it."""
+    from conftest import TEST_CONFIGS
+    cfg = pe.Qwen3Config.from_dict(dict(TEST_CONFIGS["B"], use_sliding_window=False))
+    plan = pe.config.architecture(cfg.architecture).plan(cfg)
+    w = pe.weights.random_weights(plan, 5, device="cpu")
+    rt = pe.parts.Runtime(DEV, dtype)
+    spec = plan.blocks[1]
+    lookup = pe.parts.lookup
+    pick = lambda part: {k: w[v] for k, v in part.weights.items()}
+    rope = lookup("position", "rope")(plan.positions["rope"].params, {}, rt)
+    parts = {"mixer_norm": lookup("norm", spec.mixer_norm.kind)(spec.mixer_norm.params, pick(spec.mixer_norm), rt),
+             "mixer": lookup("mixer", spec.mixer.kind)(spec.mixer.params, pick(spec.mixer), rt, positions={"rope": rope}),
+             "ffn_norm": lookup("norm", spec.ffn_norm.kind)(spec.ffn_norm.params, pick(spec.ffn_norm), rt),
+             "ffn": lookup("feed_forward", spec.ffn.kind)(spec.ffn.params, pick(spec.ffn), rt)}
+    block = lookup("arrangement", spec.arrangement)(spec, parts, rt)
+    cache = pe.cache.PagedCache({1: lookup("mixer", "attention").cache_request(spec.mixer.params)}, max_tokens=256,
+                                max_slots=2, max_seq_len=256, dtype=dtype, device=DEV)
+    slot = cache.alloc_slot()
+    S = 70
+    ctx, _ = _ctx(pe, rt, cache, [slot], [S])
+    x = torch.randn(S, cfg.hidden_size)
+    prev = (torch.randn(S, cfg.hidden_size) * 0.1).to(torch.bfloat16)             # the delta of a block before
+    stream = x.to(DEV).clone()
+    pending = block.forward(stream, prev.to(DEV, dtype), ctx, cache.view(1))
+    got = (stream + pending.float()).cpu()
+    want = plain.decoder_block(x + prev.float(), {k: v.float() for k, v in w.items()}, 1, cfg.to_dict(), None,
+                               torch.bfloat16 if dtype == torch.bfloat16 else None)
+    assert rt.status.tolist()[0] == 0
+    assert rel_err(got, want) < PTOL[dtype]
+
+
 # ---- a toy architecture with a mixer that keeps fixed-size state -------------------------------------
 @dataclass(frozen=True)
 class ToyConfig:
