@@ -1,0 +1,414 @@
+// Prefill attention on the fifth-generation tensor cores (tcgen05.mma), for bfloat16, head size 128
+// and groups of 1, 2, 4, 8 or 16 query heads per kv head.  Same contract and formulas as
+// attention_mma.cu (pygguf_engine/kv_cache.py:833, 2189-2192 masks; 756 head mapping; 836-861 online
+// softmax); other shapes keep using that file.
+//
+// A block owns 128 rows of one (sequence, kv head), a row being a (query token, head of the group)
+// pair, and walks the sequence's 64-key pages.  Roles:
+//   warp 5    TMA producer: Q once (a 3-D box [tokens][group heads][64 features] per feature half),
+//             then a K page and a V page per stage (2 stages);
+//   warp 4    MMA issuer: S = Q.K^T (128 x 64, eight k-steps of 16) into one of two S accumulators in
+//             tensor memory, and O += P.V (128 x 128, four k-steps of 16 keys) with V as an MN-major
+//             operand, so the page that TMA wrote as [keys][features] needs no transpose;
+//   warps 0-3 softmax: thread r owns row r.  It reads its S row from TMEM (tcgen05.ld), scales and
+//             masks, keeps the running maximum and sum in registers, writes P as bfloat16 into shared
+//             memory in the swizzled K-major layout the MMA reads, and rescales its O row in TMEM
+//             (tcgen05.ld / tcgen05.st) only when the maximum has grown by more than 2^8 since the last
+//             rescale (the reference of the exponentials is then moved; until then P simply carries
+//             the larger factor, which float32 sums and bfloat16 products hold without loss).
+// S of the next page is computed while the softmax of the current one runs.  All waits are bounded.
+#include "common.cuh"
+#include "tma.cuh"
+
+namespace pe {
+namespace fau {
+
+constexpr int HD = 128;        // head size
+constexpr int BM = 128;        // rows per block
+constexpr int BN = 64;         // keys per page
+constexpr int kQBytes = BM * HD * 2;          // 32 KB: two 64-feature halves of [128 rows][128 B]
+constexpr int kKVBytes = 2 * BN * HD * 2;     // 32 KB: K page then V page, each two halves of [64][128 B]
+constexpr int kPBytes = BM * BN * 2;          // 16 KB
+constexpr int kTmemCols = 256;                // S0 [0,64) S1 [64,128) O [128,256)
+constexpr float kRescaleThreshold = 8.0f;     // in log2 units
+
+struct Args {
+  __nv_bfloat16* out; long long out_ld;
+  int n_heads, n_kv_heads, group;
+  float scale_log2;
+  int window;
+  const int* seq_qstart; const int* seq_past; const int* seq_slot;
+  const int* page_table; int table_stride; int num_pages;
+  int* status;
+};
+
+// ---- tcgen05 wrappers (see gemm_umma.cu for the descriptor layouts) ------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tma::smem_addr(holder)), "r"(cols));
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols));
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tma::smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) {
+  return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// MN-major operand, 128-byte swizzle: 64 elements of the N dimension are contiguous (128 bytes); the
+// next 64 lie `lbo` bytes further; along K, rows are 128 bytes apart in groups of 8 (1024 bytes).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr, uint32_t lbo_bytes) {
+  return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::f16 instruction descriptor: float32 D, bfloat16 A and B, A K-major; b_mn: B is MN-major (bit 16).
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+      ::"r"(tma::smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(tma::smem_addr(bar)) : "memory");
+}
+
+// grid: (row tiles of 128, n_kv_heads, n_seqs), late row tiles first; block: 192 threads.
+__global__ void __launch_bounds__(192, 2)
+prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                    const __grid_constant__ CUtensorMap vmap) {
+  // All shared memory is dynamic and starts on a 1,024-byte boundary (there are no static shared
+  // variables in front of it), so that two blocks fit on an SM: tiles first, barriers behind them.
+  extern __shared__ __align__(1024) char smem[];
+  pdl_wait();
+  pdl_launch_dependents();
+  char* q_s = smem;                       // [2 halves][128 rows][128 B]
+  char* kv_s = q_s + kQBytes;             // 2 stages of (K page, V page)
+  char* p_s = kv_s + 2 * kKVBytes;        // [128 rows][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + kPBytes);
+  uint64_t& q_full = bars[0];
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = bars + 3;
+  uint64_t* s_full = bars + 5;
+  uint64_t& p_ready = bars[7];
+  uint64_t& pv_done = bars[8];
+  uint32_t& tmem_holder = *reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int& failed = *reinterpret_cast<volatile int*>(bars + 10);
+  if ((tma::smem_addr(smem) & 1023u) != 0) {   // the swizzled tiles need this alignment
+    if (threadIdx.x == 0) report(a.status, kStatusWaitTimedOut, 29, (int)(tma::smem_addr(smem) & 1023u), 0);
+    return;
+  }
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.z, kvh = blockIdx.y;
+  const int group = a.group;
+  const int q0 = a.seq_qstart[b], q_len = a.seq_qstart[b + 1] - q0, past = a.seq_past[b];
+  const int n_rows = q_len * group;
+  const int row0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BM;
+  if (row0 >= n_rows) return;
+  const int slot = a.seq_slot[b];
+  const int tok0 = row0 / group;                              // BM is a multiple of the group
+  const int last_row = min(n_rows, row0 + BM) - 1;
+  const int first_pos = past + tok0, last_pos = past + last_row / group;
+  int k_begin = 0;
+  if (a.window > 0) k_begin = max(0, first_pos - a.window + 1) / BN * BN;
+  const int k_end = last_pos + 1;
+  const int n_tiles = (k_end - k_begin + BN - 1) / BN;
+
+  if (tid == 0) {
+    tma::mbar_init(&q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      tma::mbar_init(&kv_full[s], 1);
+      tma::mbar_init(&kv_empty[s], 1);
+      tma::mbar_init(&s_full[s], 1);
+    }
+    tma::mbar_init(&p_ready, 128);
+    tma::mbar_init(&pv_done, 1);
+    failed = 0;
+    tma::fence_barrier_init();
+  }
+  if (warp == 4) tmem_alloc(&tmem_holder, kTmemCols);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = tmem_holder;
+  const uint32_t tmem_o = tmem_base + 128;
+
+  if (warp == 5) {
+    // ---- TMA producer ----
+    if (lane == 0) {
+      tma::mbar_expect_tx(&q_full, kQBytes);
+      load_3d(q_s, &qmap, 0, kvh * group, q0 + tok0, &q_full);
+      load_3d(q_s + kQBytes / 2, &qmap, 64, kvh * group, q0 + tok0, &q_full);
+      for (int j = 0; j < n_tiles && !failed; ++j) {
+        const int st = j & 1;
+        if (!tma::mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1)) {
+          report(a.status, kStatusWaitTimedOut, 20, blockIdx.x, j);
+          failed = 1;
+          break;
+        }
+        const int k0 = k_begin + j * BN;
+        const int logical = k0 / BN;
+        int page = -1;
+        if (logical < a.table_stride) page = a.page_table[(size_t)slot * a.table_stride + logical];
+        if (page < 0 || page >= a.num_pages) {
+          report(a.status, kStatusPageOutOfRange, slot, page, k0);
+          page = 0;
+        }
+        const int y = (page * a.n_kv_heads + kvh) * BN;
+        char* ks = kv_s + st * kKVBytes;
+        char* vs = ks + kKVBytes / 2;
+        tma::mbar_expect_tx(&kv_full[st], kKVBytes);
+        tma::load_2d(ks, &kmap, 0, y, &kv_full[st]);
+        tma::load_2d(ks + BN * 128, &kmap, 64, y, &kv_full[st]);
+        tma::load_2d(vs, &vmap, 0, y, &kv_full[st]);
+        tma::load_2d(vs + BN * 128, &vmap, 64, y, &kv_full[st]);
+      }
+    }
+  } else if (warp == 4) {
+    // ---- MMA issuer ----
+    if (lane == 0) {
+      const uint32_t idesc_qk = instr_desc(BM, BN, false);
+      const uint32_t idesc_pv = instr_desc(BM, HD, true);
+      const uint32_t q_addr = tma::smem_addr(q_s), p_addr = tma::smem_addr(p_s);
+      auto issue_qk = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!tma::mbar_wait(&kv_full[st], (j >> 1) & 1)) return false;
+        fence_after_sync();
+        const uint32_t k_addr = tma::smem_addr(kv_s + st * kKVBytes);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off_a = (k >> 2) * (BM * 128) + (k & 3) * 32;
+          const uint32_t off_b = (k >> 2) * (BN * 128) + (k & 3) * 32;
+          umma_bf16(tmem_base + st * BN, desc_k_major(q_addr + off_a), desc_k_major(k_addr + off_b), idesc_qk, k > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[st]);
+        return true;
+      };
+      bool ok = tma::mbar_wait(&q_full, 0);
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (j + 1 < n_tiles) ok = issue_qk(j + 1);        // S of the next page while this one's softmax runs
+        if (!ok) break;
+        if (!tma::mbar_wait(&p_ready, j & 1)) { ok = false; break; }
+        fence_after_sync();
+        const int st = j & 1;
+        const uint32_t v_addr = tma::smem_addr(kv_s + st * kKVBytes + kKVBytes / 2);
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k)
+          umma_bf16(tmem_o, desc_k_major(p_addr + k * 32), desc_mn_major(v_addr + k * 16 * 128, BN * 128), idesc_pv,
+                    (j > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&kv_empty[st]);
+        umma_commit(&pv_done);
+      }
+      if (!ok) {
+        report(a.status, kStatusWaitTimedOut, 21, blockIdx.x, blockIdx.y);
+        failed = 1;
+      }
+    }
+  } else {
+    // ---- softmax: thread r owns row r ----
+    const int r = tid;                               // 0..127; warp w reads TMEM lanes 32w..32w+31
+    const int row = row0 + r;
+    const bool live = row < n_rows;
+    const int qpos = past + row / group;
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int st = j & 1;
+      const int k0 = k_begin + j * BN;
+      if (failed || !tma::mbar_wait(&s_full[st], (j >> 1) & 1)) { ok = false; break; }
+      fence_after_sync();
+      uint32_t sv[2][32];
+      tmem_ld32(tmem_base + st * BN + lane_off, sv[0]);
+      tmem_ld32(tmem_base + st * BN + 32 + lane_off, sv[1]);
+      tmem_ld_wait();
+      float mx = -INFINITY;
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int kpos = k0 + h * 32 + c;
+          bool vis = live && kpos <= qpos;
+          if (a.window > 0) vis = vis && (kpos > qpos - a.window);
+          const float v = vis ? __uint_as_float(sv[h][c]) * a.scale_log2 : -INFINITY;
+          sv[h][c] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      // the previous P.V must be done before P is overwritten or O is touched
+      if (j > 0 && !tma::mbar_wait(&pv_done, (j - 1) & 1)) { ok = false; break; }
+      fence_after_sync();
+      // move the reference of the exponentials only when the maximum has grown a lot
+      const bool grow = mx > m_ref + kRescaleThreshold;
+      if (__any_sync(0xffffffffu, grow && j > 0 && m_ref != -INFINITY)) {
+        const float f = (grow && m_ref != -INFINITY) ? fast_exp2(m_ref - mx) : 1.0f;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t ov[32];
+          tmem_ld32(tmem_o + c + lane_off, ov);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
+          tmem_st32(tmem_o + c + lane_off, ov);
+        }
+        tmem_st_wait();
+        l *= f;
+      }
+      if (grow) m_ref = mx;
+      const float base = (m_ref == -INFINITY) ? 0.f : m_ref;
+      float sum = 0.f;
+      char* prow = p_s + r * 128;
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {   // 16-byte chunks of 8 keys
+          uint32_t w[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float p0 = fast_exp2(__uint_as_float(sv[h][c8 * 8 + 2 * i]) - base);
+            const float p1 = fast_exp2(__uint_as_float(sv[h][c8 * 8 + 2 * i + 1]) - base);
+            sum += p0 + p1;
+            w[i] = pack2(p0, p1);
+          }
+          const int chunk = h * 4 + c8;
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      l += sum;
+      tma::fence_proxy_async();           // P must be visible to the tensor core's reads
+      fence_before_sync();
+      tma::mbar_arrive(&p_ready);
+    }
+    if (ok && tma::mbar_wait(&pv_done, (n_tiles - 1) & 1)) {
+      fence_after_sync();
+      const float inv = 1.f / fmaxf(l, 1e-20f);
+      const int tok = row / group, head = kvh * group + row % group;
+      __nv_bfloat16* dst = a.out + (size_t)(q0 + tok) * a.out_ld + (size_t)head * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t ov[32];
+        tmem_ld32(tmem_o + c + lane_off, ov);
+        tmem_ld_wait();
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 o4;
+            o4.x = pack2(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
+            o4.y = pack2(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
+            o4.z = pack2(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
+            o4.w = pack2(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c + 8 * i) = o4;
+          }
+        }
+      }
+    } else {
+      if (lane == 0 && !failed) report(a.status, kStatusWaitTimedOut, 22, blockIdx.x, blockIdx.y);
+      failed = 1;
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace fau
+}  // namespace pe
+
+extern "C" int pe_attention_umma_supported(int head_dim, int n_heads, int n_kv_heads) {
+  if (head_dim != 128 || n_kv_heads <= 0 || n_heads % n_kv_heads) return 0;
+  const int g = n_heads / n_kv_heads;
+  return (g == 1 || g == 2 || g == 4 || g == 8 || g == 16) ? 1 : 0;
+}
+
+// Prefill form only (decode keeps attention_mma.cu).  q: rows of the fused q|k|v buffer, [n_tokens, q_ld].
+extern "C" int pe_attention_umma_prefill(const void* q, long long q_ld, long long n_tokens, void* out, long long out_ld,
+                                         int n_seqs, int max_q, int n_heads, int n_kv_heads, int head_dim, float scale,
+                                         int window, const int* seq_qstart, const int* seq_past, const int* seq_slot,
+                                         const int* page_table, int table_stride, int num_pages, const void* k_pages,
+                                         const void* v_pages, int* status, cudaStream_t stream) {
+  using namespace pe::fau;
+  if (n_seqs <= 0) return PE_OK;
+  if (!pe_attention_umma_supported(head_dim, n_heads, n_kv_heads)) return PE_ERR_UNSUPPORTED_SIZE;
+  if (((uintptr_t)q % 16) || (q_ld * 2) % 16 || ((uintptr_t)out % 16) || (out_ld * 2) % 16) return PE_ERR_BAD_ARGUMENT;
+  Args a;
+  a.out = (__nv_bfloat16*)out; a.out_ld = out_ld; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads;
+  a.group = n_heads / n_kv_heads; a.scale_log2 = scale * 1.4426950408889634f; a.window = window;
+  a.seq_qstart = seq_qstart; a.seq_past = seq_past; a.seq_slot = seq_slot;
+  a.page_table = page_table; a.table_stride = table_stride; a.num_pages = num_pages; a.status = status;
+  pe::tma::EncodeTiledFn fn = pe::tma::encode_fn();
+  if (fn == nullptr) return -5;
+  CUtensorMap qmap, kmap, vmap;
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)n_heads, (cuuint64_t)n_tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)q_ld * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)a.group, (cuuint32_t)(BM / a.group)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(&qmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return PE_ERR_BAD_ARGUMENT;
+  }
+  const uint64_t rows = (uint64_t)num_pages * n_kv_heads * BN;
+  int me = pe::tma::make_map_2d_bf16(&kmap, k_pages, HD, rows, HD, 64, BN);
+  if (me == 0) me = pe::tma::make_map_2d_bf16(&vmap, v_pages, HD, rows, HD, 64, BN);
+  if (me != 0) return me < 0 ? me : PE_ERR_BAD_ARGUMENT;
+  const size_t smem = kQBytes + 2 * kKVBytes + kPBytes + 128;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t ce = cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (ce != cudaSuccess) return (int)ce;
+    attr_set = true;
+  }
+  const long long tiles = ((long long)max_q * a.group + BM - 1) / BM;
+  dim3 grid((unsigned)tiles, n_kv_heads, n_seqs);
+  if (grid.y > 65535 || grid.z > 65535) return PE_ERR_UNSUPPORTED_SIZE;
+  pe::launch(prefill_umma_kernel, grid, 192, smem, stream, a, qmap, kmap, vmap);
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}

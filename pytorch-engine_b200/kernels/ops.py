@@ -222,6 +222,26 @@ def gemm_umma(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, status: 
     _count(1)
 
 
+def attention_umma_supported(dtype: torch.dtype, head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
+    """Whether the tcgen05 prefill attention (csrc/attention_umma.cu) takes this shape."""
+    return dtype == torch.bfloat16 and bool(library().pe_attention_umma_supported(head_dim, n_heads, n_kv_heads))
+
+
+def attention_umma_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_q: int, n_heads: int, n_kv_heads: int,
+                           head_dim: int, scale: float, window: int, seq_qstart: torch.Tensor, seq_past: torch.Tensor,
+                           seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int, k_pages: torch.Tensor,
+                           v_pages: torch.Tensor, status: torch.Tensor) -> None:
+    """Prefill attention on tcgen05 (bfloat16, head size 128, group 1/2/4/8/16); ``q`` holds the step's
+    query rows (the first ``n_heads * head_dim`` features of each row of the fused q|k|v buffer)."""
+    _need(q.stride(-1) == 1 and out.stride(-1) == 1, "attention: rows must be contiguous")
+    _need(q.dtype == out.dtype == k_pages.dtype == torch.bfloat16, "attention_umma: bfloat16 tensors only")
+    check(library().pe_attention_umma_prefill(
+        _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), n_seqs, max_q, n_heads, n_kv_heads, head_dim,
+        float(scale), int(window), _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot), _ptr(page_table),
+        page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages), _ptr(status), _stream()), "attention_umma_prefill")
+    _count(1)
+
+
 def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float, seed: int,
            row_request: torch.Tensor, row_step: torch.Tensor, out_tokens: torch.Tensor) -> None:
     _need(logits.dtype == torch.float32 and logits.stride(-1) == 1, "sample: float32 logits with contiguous rows")

@@ -82,6 +82,9 @@ class GQAttention:
         # the generic float32-arithmetic kernels otherwise
         self.use_mma = runtime.is_cuda and ops.attention_mma_supported(runtime.dtype, self.head_dim, self.n_heads,
                                                                        self.n_kv_heads)
+        # prefill on tcgen05 where that kernel takes the shape (bfloat16, head size 128, group 1/2/4/8/16)
+        self.use_umma_prefill = runtime.is_cuda and ops.attention_umma_supported(runtime.dtype, self.head_dim,
+                                                                                  self.n_heads, self.n_kv_heads)
 
     def forward(self, x: torch.Tensor, ctx, view, writes_cache: bool = True) -> torch.Tensor:
         rt = self.runtime
@@ -105,6 +108,12 @@ class GQAttention:
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx, view) -> None:
         """Attention of the step's queries (the first ``n_heads*head_dim`` features of each row of
         ``q``) over the cache of their sequences."""
+        if self.use_umma_prefill and not ctx.decode:
+            ops.attention_umma_prefill(
+                q, out, ctx.n_seqs, ctx.max_q, self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.window,
+                ctx.seq_qstart, ctx.seq_past, ctx.seq_slot, view.page_table, view.num_pages, view.k_pages, view.v_pages,
+                self.runtime.status)
+            return
         scratch = None
         max_splits = 0
         split_keys = SPLIT_KEYS

@@ -53,8 +53,13 @@ TEST_CONFIGS = {
               num_key_value_heads=2, head_dim=64, intermediate_size=304, vocab_size=300, rope_theta=100000.0,
               rms_norm_eps=2e-6, tie_word_embeddings=False, max_position_embeddings=1024,
               use_sliding_window=True, sliding_window=70, max_window_layers=1),
+    # E has the head size of the tcgen05 prefill attention (128), a group of 4, full and windowed layers
+    "E": dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=144, num_attention_heads=4,
+              num_key_value_heads=1, head_dim=128, intermediate_size=272, vocab_size=333, rope_theta=250000.0,
+              rms_norm_eps=4e-6, tie_word_embeddings=True, max_position_embeddings=1024,
+              use_sliding_window=True, sliding_window=90, layer_types=["sliding_attention", "full_attention"]),
 }
-TEST_SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
+TEST_SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
 
 
 def make_model_folder(pe, tmp_path_factory, key, sharpen=None):

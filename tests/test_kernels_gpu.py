@@ -319,6 +319,61 @@ def test_attention_mma_prefill(ops, nh, nkv, d, window):
     assert rel_err(out.float().cpu().view(N, nh, d), want) < ATT_TOL[dtype]
 
 
+@pytest.mark.parametrize("nh,nkv", [(32, 8), (16, 1), (3, 3), (8, 4), (16, 2)])
+@pytest.mark.parametrize("window", [0, 37, 150])
+def test_attention_umma_prefill(ops, nh, nkv, window):
+    """The tcgen05 prefill attention against the plain formula (head size 128, groups 4, 16, 1, 2, 8)."""
+    torch.manual_seed(25)
+    d, dtype = 128, torch.bfloat16
+    assert ops.attention_umma_supported(dtype, d, nh, nkv)
+    lens = [300, 1, 77, 64, 130, 513]
+    pasts = [0, 0, 50, 0, 127, 0]
+    q_lens = [L - p for L, p in zip(lens, pasts)]
+    ps = PagedSetup(lens, nkv, d, dtype, seed=25, key_scale=2.0)
+    N = sum(q_lens)
+    ld = nh * d + 2 * nkv * d
+    q_all = torch.randn(N, ld, device=DEV).to(dtype)
+    out = torch.zeros(N, nh * d, device=DEV, dtype=dtype)
+    qstart = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    past_t = torch.tensor(pasts, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    st = _status()
+    ops.attention_umma_prefill(q_all, out, len(lens), max(q_lens), nh, nkv, d, scale, window, qstart, past_t, ps.seq_slot,
+                               ps.table, ps.num_pages, ps.k_pages, ps.v_pages, st)
+    torch.cuda.synchronize()
+    assert st.tolist()[0] == 0, st.tolist()
+    qs, o = [], 0
+    for n in q_lens:
+        qs.append(q_all[o:o + n, : nh * d].cpu().view(n, nh, d)); o += n
+    want = _plain_attention(ps, qs, pasts, nh, scale, window or None)
+    assert rel_err(out.float().cpu().view(N, nh, d), want) < ATT_TOL[dtype]
+
+
+def test_attention_umma_prefill_rescales_when_the_maximum_grows(ops):
+    """Scores that grow by far more than 2^8 along the sequence: the reference of the exponentials
+    must move and the accumulated output be rescaled."""
+    nh, nkv, d, dtype = 4, 1, 128, torch.bfloat16
+    L = 400
+    ps = PagedSetup([L], nkv, d, dtype, seed=26, key_scale=0.1)
+    probe = torch.randn(d)
+    probe = probe / probe.norm()
+    q_all = (probe * 6.0).repeat(L, nh).to(dtype).to(DEV)                 # every query points along `probe`
+    for pos in range(L):                                                   # keys grow along `probe` with the position
+        page = int(ps.table[ps.slots[0], pos // 64])
+        ps.k_pages[page, 0, pos % 64] += (probe * (pos / 10.0)).to(dtype).to(DEV)
+    ps.k[0] = torch.stack([ps.k_pages[int(ps.table[ps.slots[0], p // 64]), :, p % 64].cpu() for p in range(L)])
+    out = torch.zeros(L, nh * d, device=DEV, dtype=dtype)
+    qstart = torch.tensor([0, L], dtype=torch.int32, device=DEV)
+    past_t = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    st = _status()
+    ops.attention_umma_prefill(q_all, out, 1, L, nh, nkv, d, scale, 0, qstart, past_t, ps.seq_slot, ps.table,
+                               ps.num_pages, ps.k_pages, ps.v_pages, st)
+    assert st.tolist()[0] == 0
+    want = _plain_attention(ps, [q_all.cpu().view(L, nh, d)], [0], nh, scale, None)
+    assert rel_err(out.float().cpu().view(L, nh, d), want) < ATT_TOL[dtype]
+
+
 @pytest.mark.parametrize("nh,nkv,d", MMA_SHAPES)
 @pytest.mark.parametrize("window", [0, 300])
 def test_attention_mma_decode(ops, nh, nkv, d, window):

@@ -13,7 +13,7 @@ import plain_qwen3 as plain
 from conftest import ROOT, TEST_CONFIGS, TOL, rel_err
 
 pytestmark = pytest.mark.gpu
-KEYS = ["A", "B", "C", "D"]
+KEYS = ["A", "B", "C", "D", "E"]
 DTYPES = ["float32", "bfloat16"]
 
 
@@ -207,7 +207,7 @@ def test_long_decoding_and_first_tokens(pe, engines, oracles, tmp_path, key, dty
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("key", ["B", "D"])
+@pytest.mark.parametrize("key", ["B", "D", "E"])
 def test_random_cuts_into_steps(pe, engines, oracles, tmp_path, key, dtype):
     """Three requests run together; every step brings each of them a random number of its next tokens
     (one, a few, or many; a request that has none left sits the step out).  Whatever the cuts, the
