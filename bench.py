@@ -266,7 +266,7 @@ def main():
 
     if not args.no_e2e:
         # through the public API: real prompts, host token ids in and out at every step
-        steps_e = max(8, min(K, 32))
+        steps_e = max(8, K)
         plen = ctx - steps_e - 1
         prompts = [torch.randint(0, vocab, (plen,), generator=gen).tolist() for _ in range(B)]
         params = pe.SamplingParams.greedy_params(max_tokens=steps_e + 1)

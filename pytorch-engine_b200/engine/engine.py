@@ -58,6 +58,19 @@ class _LoopBackend:
     def step(self, entries):
         return self.engine.runner.step(entries, check=False)
 
+    def launch_decode(self, slots, tokens, params, seed, requests, steps):
+        """Launch one decode step and its draw without waiting.  ``tokens``: the input tokens as a list,
+        or None to take the tokens that the previous launch drew (still on the device).  Returns a handle
+        with ``result() -> tokens``, or None if this cannot be done without the host in between."""
+        eng = self.engine
+        if tokens is None:
+            if not eng.runner.can_step_from_device_tokens(len(slots)):
+                return None
+            logits = eng.runner.step_from_device_tokens(slots, eng.runtime.token_area)
+        else:
+            logits = eng.runner.step([StepEntry(s, (t,), (0,)) for s, t in zip(slots, tokens)], check=False)
+        return eng.sampler.sample_async(logits, params, seed, requests, steps)
+
 
 class Engine:
     def __init__(self, model_path: Optional[str] = None, *, dtype: Union[str, torch.dtype] = "bfloat16",
@@ -149,17 +162,19 @@ class Engine:
             return [list(p) for p in prompt_or_prompts], True
         return [list(prompt_or_prompts)], False
 
-    @torch.inference_mode()
+    @torch.no_grad()
     def generate(self, prompt_or_ids, sampling: Optional[SamplingParams] = None):
         """Token ids in, ``GenerationResult`` out; a list of prompts gives a list of results."""
         prompts, many = self._as_batch(prompt_or_ids)
         results = self.loop.generate(prompts, sampling)
         return results if many else results[0]
 
-    @torch.inference_mode()
     def stream_tokens(self, prompt_or_ids, sampling: Optional[SamplingParams] = None) -> Iterator[StreamChunk]:
         prompts, _ = self._as_batch(prompt_or_ids)
-        yield from self.loop.stream(prompts, sampling)
+        # no_grad rather than inference_mode: buffers made here are also written by later calls of
+        # step(), which may come from outside any such context
+        with torch.no_grad():
+            yield from self.loop.stream(prompts, sampling)
 
     # ---- reports -----------------------------------------------------------------------------
     def memory_report(self) -> Dict[str, float]:

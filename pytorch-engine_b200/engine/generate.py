@@ -15,7 +15,10 @@ step (685).
 
 The loop decides; it does not compute.  ``backend`` supplies ``alloc_slot()``, ``free_slot(slot)``,
 ``free_pages()``, ``step(entries) -> logits`` and ``sample(logits, params, seed, requests, steps,
-recent) -> tokens``, so the decisions can be tested without a GPU.
+recent) -> tokens``, so the decisions can be tested without a GPU.  A backend may also offer
+``launch_decode(slots, tokens_or_None, params, seed, requests, steps) -> handle`` (``handle.result()``
+gives the drawn tokens): the loop then keeps one decode step queued ahead of the one whose tokens it
+is reading, so the device never waits for the host between steps.
 """
 from __future__ import annotations
 
@@ -126,6 +129,7 @@ class GenerationLoop:
     def _run_batch(self, batch: List[int], prompts, params: SamplingParams, stop_ids, seed: int) -> Iterator[StreamChunk]:
         be = self.backend
         live: List[_Live] = []
+        launch = getattr(be, "launch_decode", None) if params.repetition_penalty == 1.0 else None
         try:
             for i in batch:
                 live.append(_Live(request=i, slot=be.alloc_slot(), prompt=prompts[i],
@@ -135,9 +139,11 @@ class GenerationLoop:
             tokens = self._draw(logits, live, params, seed)
             prefill_s = time.perf_counter() - t0
             t_decode = time.perf_counter()
-            while True:
-                still: List[_Live] = []
-                for s, tok in zip(live, tokens):
+
+            def take_in(seqs: List[_Live], toks: List[int], free_now: bool):
+                """Append each sequence's new token or end the sequence; returns (chunks, still, ended)."""
+                chunks, still, ended = [], [], []
+                for s, tok in zip(seqs, toks):
                     reason = None
                     if tok in stop_ids:
                         reason = "stop"
@@ -147,20 +153,63 @@ class GenerationLoop:
                             reason = "length"
                     if reason is None:
                         still.append(s)
-                        yield StreamChunk(s.request, tok)
+                        chunks.append(StreamChunk(s.request, tok))
                     else:
-                        be.free_slot(s.slot)
-                        s.slot = -1
+                        ended.append(s)
+                        if free_now:
+                            be.free_slot(s.slot)
+                            s.slot = -1
                         stats = GenerationResult(
                             token_ids=list(s.generated), prompt_tokens=len(s.prompt),
                             completion_tokens=len(s.generated), finish_reason=reason, prefill_time_s=prefill_s,
                             decode_time_s=time.perf_counter() - t_decode)
-                        yield StreamChunk(s.request, tok, reason, stats)
-                live = still
-                if not live:
-                    break
-                logits = be.step([StepEntry(s.slot, (s.generated[-1],), (0,)) for s in live])
-                tokens = self._draw(logits, live, params, seed)
+                        chunks.append(StreamChunk(s.request, tok, reason, stats))
+                return chunks, still, ended
+
+            def give_back(seqs: List[_Live]) -> None:
+                for s in seqs:
+                    if s.slot >= 0:
+                        be.free_slot(s.slot)
+                        s.slot = -1
+
+            chunks, live, _ = take_in(live, tokens, True)
+            yield from chunks
+            pending = None      # a launched decode step for `live` whose tokens have not been read yet
+            while live:
+                if launch is None:
+                    logits = be.step([StepEntry(s.slot, (s.generated[-1],), (0,)) for s in live])
+                    tokens = self._draw(logits, live, params, seed)
+                    chunks, live, _ = take_in(live, tokens, True)
+                    yield from chunks
+                    continue
+                if pending is None:
+                    pending = launch([s.slot for s in live], [s.generated[-1] for s in live], params, seed,
+                                     [s.request for s in live], [len(s.generated) for s in live])
+                # One step ahead: if no sequence can end by length with the pending token, the step after it is
+                # launched now, fed on the device with the tokens the pending step draws.  Only a stop token
+                # can then make that work partly useless (the rows of sequences that have just ended).
+                ahead = None
+                if all(len(s.generated) + 1 < s.max_new for s in live):
+                    ahead = launch([s.slot for s in live], None, params, seed, [s.request for s in live],
+                                   [len(s.generated) + 1 for s in live])
+                tokens = pending.result()
+                pending = None
+                if ahead is None:
+                    chunks, live, _ = take_in(live, tokens, True)
+                    yield from chunks
+                    continue
+                # the slots of sequences that end now stay taken until the step that is in flight is through
+                chunks, still, ended = take_in(live, tokens, False)
+                yield from chunks
+                if not ended:
+                    pending = ahead
+                    continue
+                tokens_ahead = ahead.result()
+                give_back(ended)
+                keep = {id(s) for s in still}
+                pairs = [(s, t) for s, t in zip(live, tokens_ahead) if id(s) in keep]
+                chunks, live, _ = take_in([s for s, _ in pairs], [t for _, t in pairs], True)
+                yield from chunks
         finally:
             for s in live:
                 if s.slot >= 0:

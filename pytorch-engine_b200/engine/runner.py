@@ -86,6 +86,27 @@ class ModelRunner:
             self.runtime.raise_on_status()
         return logits
 
+    def can_step_from_device_tokens(self, n_seqs: int) -> bool:
+        return self.cuda_graphs and n_seqs in self._graphs
+
+    def step_from_device_tokens(self, slots: Sequence[int], device_tokens: torch.Tensor) -> torch.Tensor:
+        """One decode step for ``slots`` whose input tokens are ``device_tokens`` (int32, on the device, one
+        per slot): the graph captured for this many sequences is replayed with its token buffer filled by
+        a device-to-device copy, so the host never sees the tokens on the way in."""
+        n = len(slots)
+        g = self._graphs[n]
+        pasts = [self.cache.length(s) for s in slots]
+        for s, past in zip(slots, pasts):
+            self.cache.reserve(s, past + 1)
+        g.ctx.tokens.copy_(device_tokens[:n], non_blocking=True)
+        self.stager.send(list(slots) + pasts + list(range(n + 1)) + list(range(n)), g.ctx.meta[n:])
+        g.graph.replay()
+        ops.count_replay(g.launches)
+        for s, past in zip(slots, pasts):
+            self.cache.commit(s, past + 1)
+        self.steps_run += 1
+        return g.logits
+
     def _step_graph(self, meta_ints, n_seqs: int) -> torch.Tensor:
         g = self._graphs.get(n_seqs)
         if g is None:

@@ -23,6 +23,33 @@ STATUS_MESSAGES = {
 }
 
 
+class PendingTokens:
+    """Tokens (and the status word) on their way to the host; ``result()`` waits and returns the tokens,
+    raising if a kernel reported an error."""
+
+    def __init__(self, runtime: "Runtime") -> None:
+        self.runtime = runtime
+        self.host = torch.empty(4 + runtime.max_result_rows, dtype=torch.int32, pin_memory=runtime.is_cuda)
+        self.event = torch.cuda.Event() if runtime.is_cuda else None
+        self.n = 0
+
+    def start(self, n: int) -> None:
+        self.n = n
+        self.host[:4 + n].copy_(self.runtime._status_and_tokens[:4 + n], non_blocking=True)
+        if self.event is not None:
+            self.event.record()
+
+    def result(self):
+        if self.event is not None:
+            self.event.synchronize()
+        vals = self.host[:4 + self.n].tolist()
+        if vals[0] != 0:
+            self.runtime.status.zero_()
+            msg = STATUS_MESSAGES.get(vals[0], "kernel status {0}").format(*vals[1:4])
+            raise KernelError(f"a kernel reported an error during the step: {msg}")
+        return vals[4:]
+
+
 class Runtime:
     def __init__(self, device, dtype: torch.dtype) -> None:
         self.device = torch.device(device)
@@ -37,6 +64,8 @@ class Runtime:
         self.status = self._status_and_tokens[:4]
         self.token_area = self._status_and_tokens[4:]
         self._host_result = None
+        self._pending_ring = None
+        self._pending_next = 0
         self._adopted: Dict[Tuple[int, torch.dtype], torch.Tensor] = {}
         self.gemm_backend = None  # a callable (x, weight, out, out_dtype) -> tensor or None that takes over products
         self.own_small_gemm = True  # products with few rows run on csrc/gemm_smallm.cu
@@ -95,6 +124,18 @@ class Runtime:
             msg = STATUS_MESSAGES.get(vals[0], "kernel status {0}").format(*vals[1:4])
             raise KernelError(f"a kernel reported an error during the step: {msg}")
         return vals[4:]
+
+    def fetch_tokens_async(self, n: int) -> "PendingTokens":
+        """Start the copy of the status word and the first ``n`` ints of ``token_area`` to the host and
+        return at once; ``result()`` of the returned handle waits for it.  The device may go on and
+        overwrite ``token_area`` meanwhile: the copy is ordered before whatever is launched next."""
+        if self._pending_ring is None:
+            self._pending_ring = [PendingTokens(self) for _ in range(4)]
+            self._pending_next = 0
+        h = self._pending_ring[self._pending_next]
+        self._pending_next = (self._pending_next + 1) % len(self._pending_ring)
+        h.start(n)
+        return h
 
     # ---- matrix product ----------------------------------------------------------------------
     def linear(self, x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,

@@ -19,6 +19,34 @@ class Sampler:
         self.runtime = runtime
         self._stager = None
 
+    def _launch_into_token_area(self, logits, params, seed, requests, steps) -> None:
+        from ..engine.batch import PinnedStager
+        rt = self.runtime
+        n = logits.shape[0]
+        if self._stager is None:
+            self._stager = PinnedStager(self.device)
+            # two halves used in turn: a launched sampler may still read one while the next is being filled
+            self._meta = torch.empty(2, 2 * rt.max_result_rows, dtype=torch.int32, device=self.device)
+            self._meta_turn = 0
+        self._meta_turn ^= 1
+        meta = self._meta[self._meta_turn, :2 * n]
+        self._stager.send(list(requests) + list(steps), meta)
+        ops.sample(logits, params.temperature, params.top_k, params.top_p, params.min_p, seed, meta[:n], meta[n:],
+                   rt.token_area[:n])
+
+    def sample_async(self, logits: torch.Tensor, params: SamplingParams, seed: int, requests: Sequence[int],
+                     steps: Sequence[int]):
+        """Launch the draw and the copy of its tokens to the host; returns a handle whose ``result()``
+        waits for them.  The tokens also stay in the runtime's token area on the device, where the next
+        decode step can take them from without the host in between.  (No repetition penalty here: it
+        needs the token history on the host.)"""
+        rt = self.runtime
+        n = logits.shape[0]
+        if rt is None or n > rt.max_result_rows:
+            raise ValueError("sample_async needs a runtime and at most %d rows" % (rt.max_result_rows if rt else 0))
+        self._launch_into_token_area(logits, params, seed, requests, steps)
+        return rt.fetch_tokens_async(n)
+
     def sample(self, logits: torch.Tensor, params: SamplingParams, seed: int, requests: Sequence[int],
                steps: Sequence[int], recent: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
         """One token per row of ``logits``.  ``requests[r]`` and ``steps[r]`` key row r's random
@@ -39,14 +67,7 @@ class Sampler:
             ops.repetition_penalty(logits, rec.to(self.device), cnt.to(self.device), params.repetition_penalty)
         rt = self.runtime
         if rt is not None and n <= rt.max_result_rows:
-            from ..engine.batch import PinnedStager
-            if self._stager is None:
-                self._stager = PinnedStager(self.device)
-                self._meta = torch.empty(2 * rt.max_result_rows, dtype=torch.int32, device=self.device)
-            meta = self._meta[:2 * n]
-            self._stager.send(list(requests) + list(steps), meta)
-            out = rt.token_area[:n]
-            ops.sample(logits, params.temperature, params.top_k, params.top_p, params.min_p, seed, meta[:n], meta[n:], out)
+            self._launch_into_token_area(logits, params, seed, requests, steps)
             return rt.fetch_tokens(n)
         meta = torch.tensor([list(requests), list(steps)], dtype=torch.int32).to(self.device)
         out = torch.empty((n,), dtype=torch.int32, device=self.device)

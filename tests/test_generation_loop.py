@@ -131,3 +131,75 @@ def test_sampling_params_validate(pe):
             pe.SamplingParams(**bad).validate()
     d = pe.SamplingParams()
     assert (d.max_tokens, d.temperature, d.top_p, d.top_k, d.min_p, d.repetition_penalty) == (512, 0.7, 0.95, 40, 0.05, 1.0)
+
+
+class AheadBackend(FakeBackend):
+    """A backend that can launch decode steps without waiting (``launch_decode``).  It checks what the
+    loop may and may not do: feed a step from the device only right after a launch for the same slots,
+    and never give a slot back while a launched step that uses it has not been waited for."""
+
+    def __init__(self, scripts, pages=1000):
+        super().__init__(scripts, pages)
+        self.launches = []          # (slots, tokens or None, requests, steps)
+        self.in_flight = []         # handles not yet waited for
+        self.last_slots = None
+
+    class Handle:
+        def __init__(self, be, slots, toks):
+            self.be, self.slots, self.toks, self.done = be, list(slots), toks, False
+
+        def result(self):
+            assert self.be.in_flight and self.be.in_flight[0] is self, "steps are waited for in launch order"
+            self.be.in_flight.pop(0)
+            self.done = True
+            return self.toks
+
+    def free_slot(self, s):
+        assert all(s not in h.slots for h in self.in_flight), "a slot was given back under a step in flight"
+        super().free_slot(s)
+
+    def launch_decode(self, slots, tokens, params, seed, requests, steps):
+        assert all(s in self.held for s in slots)
+        if tokens is None:
+            assert self.last_slots == list(slots), "device tokens belong to the launch just before, same slots"
+        self.launches.append((list(slots), None if tokens is None else list(tokens), list(requests), list(steps)))
+        self.last_slots = list(slots)
+        # a sequence that has ended may still be in a step launched ahead: its draw is never looked at
+        toks = [self.scripts[r][k] if k < len(self.scripts[r]) else -1 for r, k in zip(requests, steps)]
+        h = self.Handle(self, slots, toks)
+        self.in_flight.append(h)
+        return h
+
+
+def test_one_step_ahead_gives_the_same_tokens(pe):
+    scripts = {0: [10, 11, 99, 55, 56], 1: [20, 21, 22, 23, 24, 25], 2: [99], 3: [30, 31, 32, 99, 1, 2]}
+    prompts = [[1, 2, 3], [4], [6, 7], [8]]
+    params = pe.SamplingParams(max_tokens=5, temperature=0.0)
+    plain_be, ahead_be = FakeBackend(scripts), AheadBackend(scripts)
+    want = _loop(pe, plain_be, max_batch=4).generate(prompts, params)
+    got = _loop(pe, ahead_be, max_batch=4).generate(prompts, params)
+    assert [r.token_ids for r in got] == [r.token_ids for r in want] == [[10, 11], [20, 21, 22, 23, 24], [], [30, 31, 32]]
+    assert [r.finish_reason for r in got] == ["stop", "length", "stop", "stop"]
+    assert not ahead_be.held and not ahead_be.in_flight
+    # steps fed from the device exist, and none was launched when a sequence was sure to end by length
+    assert any(t is None for _, t, _, _ in ahead_be.launches)
+    for slots, toks, reqs, steps in ahead_be.launches:
+        if toks is None:
+            assert all(k + 1 <= 5 - 1 for k in steps)
+    # the tokens a launch is fed from the host are the sequences' last tokens
+    first = ahead_be.launches[0]
+    assert first[1] == [10, 20, 30] and first[2] == [0, 1, 3] and first[3] == [1, 1, 1]
+
+
+def test_one_step_ahead_is_not_used_with_a_repetition_penalty(pe):
+    be = AheadBackend({0: [10, 11, 12]})
+    res = _loop(pe, be).generate([[1]], pe.SamplingParams(max_tokens=3, temperature=0.0, repetition_penalty=1.3))
+    assert res[0].token_ids == [10, 11, 12] and not be.launches
+
+
+def test_one_step_ahead_stream_order_and_stats(pe):
+    be = AheadBackend({0: [10, 11, 12, 13], 1: [20, 99]})
+    chunks = list(_loop(pe, be).stream([[1], [2]], pe.SamplingParams(max_tokens=4, temperature=0.0)))
+    assert [(c.request, c.token_id, c.finish_reason) for c in chunks] == [
+        (0, 10, None), (1, 20, None), (0, 11, None), (1, 99, "stop"), (0, 12, None), (0, 13, "length")]
+    assert chunks[-1].stats.token_ids == [10, 11, 12, 13]

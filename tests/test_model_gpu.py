@@ -286,6 +286,23 @@ def test_greedy_generation_through_the_entry_point(pe, engines, oracles, key, dt
     assert single.token_ids == results[1].token_ids
 
 
+def test_generate_and_step_share_an_engine(pe, engines, oracles):
+    """generate() and step() on the same engine, in either order, inside or outside torch's no-grad
+    contexts: the buffers one call makes are written by the other."""
+    cfg, w = oracles["D", "bfloat16"]
+    eng = engines("D", "bfloat16")
+    prompt = _tokens(cfg["vocab_size"], 20, 63)
+    first = eng.generate([prompt, prompt[:7]], pe.SamplingParams.greedy_params(max_tokens=5))
+    s = eng.alloc_slot()
+    lg = eng.step([pe.StepEntry(s, prompt, (19,))])
+    lg2 = eng.step([pe.StepEntry(s, [first[0].token_ids[0]], (0,))])
+    eng.free_slot(s)
+    assert int(lg[0].argmax()) == first[0].token_ids[0] and int(lg2[0].argmax()) == first[0].token_ids[1]
+    with torch.inference_mode():
+        again = eng.generate([prompt, prompt[:7]], pe.SamplingParams.greedy_params(max_tokens=5))
+    assert [r.token_ids for r in again] == [r.token_ids for r in first]
+
+
 def test_stop_token_and_context_limit(pe, engines, oracles):
     cfg, w = oracles["A"]
     eng = engines("A", "float32")
