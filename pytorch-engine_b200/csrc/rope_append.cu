@@ -203,6 +203,130 @@ __global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
   }
 }
 
+// The same for bfloat16 rows with 16-byte accesses: head sizes that are multiples of 16 up to 256,
+// the whole head rotated, everything 16-byte aligned.  A head takes head_dim / 8 lanes, so a warp
+// holds several heads; the lane that holds features [8i, 8i + 8) of the first half trades its
+// normalised values with the lane that holds the matching features of the second half.  A block
+// walks `tokens_per_block` tokens so that the per-token index loads overlap.
+__global__ void __launch_bounds__(256) qk_norm_rope_append_vec8_kernel(RopeAppendArgs a, int lanes_per_head,
+                                                                        int tokens_per_block) {
+  pdl_wait();
+  pdl_launch_dependents();
+  typedef __nv_bfloat16 T;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int lph = lanes_per_head, heads_per_warp = 32 / lph;
+  const int sub = lane / lph, li = lane - sub * lph;
+  const int total_heads = a.n_heads + 2 * a.n_kv_heads;
+  const int head = (blockIdx.y * (blockDim.x >> 5) + warp) * heads_per_warp + sub;
+  const bool active = sub < heads_per_warp && head < total_heads;
+  const int d = a.head_dim;
+  const bool is_q = head < a.n_heads;
+  const bool is_k = !is_q && head < a.n_heads + a.n_kv_heads;
+  const bool is_v = !is_q && !is_k;
+  const int kv_head = is_k ? head - a.n_heads : head - a.n_heads - a.n_kv_heads;
+  const int half_l = lph >> 1;
+  const bool second = li >= half_l;
+  const int j = 8 * (second ? li - half_l : li);  // this lane's place in a row of the angle tables
+  const int partner = lane + (second ? -half_l : half_l);
+  const bool pow2 = (lph & (lph - 1)) == 0;
+  const bool rotate = a.cos_table != nullptr && a.rotary_dim > 0;
+  const float* w = is_q ? a.q_norm_w : a.k_norm_w;
+  float wv[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) wv[e] = 1.f;
+  if (active && !is_v && w) {
+    const float4 w0 = *reinterpret_cast<const float4*>(w + 8 * li), w1 = *reinterpret_cast<const float4*>(w + 8 * li + 4);
+    wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+  }
+  for (int i = 0; i < tokens_per_block; ++i) {
+    const int t = blockIdx.x * tokens_per_block + i;
+    if (t >= a.n_tokens) break;
+    T* row = (T*)a.qkv + (size_t)t * a.ld + (size_t)head * d + 8 * li;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (active) raw = *reinterpret_cast<const uint4*>(row);
+    const int pos = a.token_pos[t];
+    T* cache_row = nullptr;
+    if (active && !is_q && a.write_cache) {
+      const int b = a.token_seq[t];
+      const int slot = a.seq_slot[b];
+      const int logical = pos / kPageTokens;
+      if (pos < 0 || logical >= a.table_stride) {
+        if (li == 0) report(a.status, kStatusPositionOutOfRange, t, pos, a.table_stride * kPageTokens);
+      } else {
+        const int page = a.page_table[(size_t)slot * a.table_stride + logical];
+        if (page < 0 || page >= a.num_pages) {
+          if (li == 0) report(a.status, kStatusPageOutOfRange, t, page, a.num_pages);
+        } else {
+          T* base = (T*)(is_k ? a.k_pages : a.v_pages);
+          const int off = pos % kPageTokens;
+          T* head_row = base + (((size_t)page * a.n_kv_heads + kv_head) * kPageTokens + off) * d;
+          cache_row = head_row + 8 * li;
+          // clear the rest of the page (see the kernel above for when and why)
+          const int q_end = a.seq_qstart[b + 1];
+          if (t + 1 == q_end && off + 1 < kPageTokens && (off == 0 || q_end - a.seq_qstart[b] > 1)) {
+            uint4* r4 = reinterpret_cast<uint4*>(head_row + d);
+            const size_t n4 = (size_t)(kPageTokens - 1 - off) * d / 8;
+            for (size_t x = li; x < n4; x += lph) r4[x] = make_uint4(0, 0, 0, 0);
+          }
+        }
+      }
+    }
+    float x[8];
+    {
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        x[2 * e] = f.x;
+        x[2 * e + 1] = f.y;
+      }
+    }
+    {
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+      if (pow2) {
+        for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      } else {
+        float total = 0.f;
+        for (int l = 0; l < lph; ++l) total += __shfl_sync(0xffffffffu, ss, (sub * lph + l) & 31);
+        ss = total;
+      }
+      if (!is_v && w != nullptr) {
+        const float inv = rsqrtf(ss / (float)d + a.eps);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = x[e] * inv * wv[e];
+      }
+    }
+    float other[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) other[e] = __shfl_sync(0xffffffffu, x[e], partner & 31);
+    if (active && !is_v && rotate) {
+      if (pos < 0 || pos >= a.table_rows) {
+        if (li == 0) report(a.status, kStatusPositionOutOfRange, t, pos, a.table_rows);
+        continue;
+      }
+      const float* cs = a.cos_table + (size_t)pos * (d / 2) + j;
+      const float* sn = a.sin_table + (size_t)pos * (d / 2) + j;
+      const float4 c0 = *reinterpret_cast<const float4*>(cs), c1 = *reinterpret_cast<const float4*>(cs + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(sn), s1 = *reinterpret_cast<const float4*>(sn + 4);
+      const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = second ? x[e] * cv[e] + other[e] * sv[e] : x[e] * cv[e] - other[e] * sv[e];
+    }
+    if (!active) continue;
+    uint4 out = raw;
+    if (!is_v) {
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
+      *reinterpret_cast<uint4*>(row) = out;
+    }
+    if (cache_row) *reinterpret_cast<uint4*>(cache_row) = out;
+  }
+}
+
 }  // namespace pe
 
 extern "C" int pe_batch_expand(const int* seq_qstart, const int* seq_past, int n_seqs, int* token_seq, int* token_pos,
@@ -240,6 +364,18 @@ extern "C" int pe_qk_norm_rope_append(int dtype, void* qkv, long long ld, int n_
                      ((uintptr_t)k_pages % (2 * esz) == 0) && ((uintptr_t)v_pages % (2 * esz) == 0) &&
                      ((uintptr_t)cos_table % 8 == 0) && ((uintptr_t)sin_table % 8 == 0) &&
                      ((uintptr_t)q_norm_w % 8 == 0) && ((uintptr_t)k_norm_w % 8 == 0);
+  const bool vec8 = dtype == PE_BF16 && head_dim % 16 == 0 && head_dim <= 256 && (rotary_dim == head_dim || cos_table == nullptr) &&
+                    ld % 8 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0 &&
+                    (uintptr_t)cos_table % 16 == 0 && (uintptr_t)sin_table % 16 == 0 && (uintptr_t)q_norm_w % 16 == 0 &&
+                    (uintptr_t)k_norm_w % 16 == 0;
+  if (vec8 && n_tokens >= 256) {  // measured: with a few tokens (decode) the kernel above is the faster one
+    const int lph = head_dim / 8, heads_per_block = 8 * (32 / lph), tokens_per_block = 4;
+    dim3 g((n_tokens + tokens_per_block - 1) / tokens_per_block, (total_heads + heads_per_block - 1) / heads_per_block);
+    if (g.y > 65535) return PE_ERR_UNSUPPORTED_SIZE;
+    pe::launch(pe::qk_norm_rope_append_vec8_kernel, g, 256, 0, stream, a, lph, tokens_per_block);
+    PE_LAUNCH_CHECK();
+    return PE_OK;
+  }
   if (dtype == PE_F32) {
     if (pairs) pe::launch(pe::qk_norm_rope_append_kernel<float, true>, grid, warps * 32, 0, stream, a);
     else pe::launch(pe::qk_norm_rope_append_kernel<float, false>, grid, warps * 32, 0, stream, a);

@@ -132,11 +132,13 @@ class PagedSetup:
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nh,nkv,d,rot", [(4, 2, 16, 16), (6, 2, 32, 32), (5, 5, 48, 48), (8, 1, 128, 64), (3, 3, 80, 80)])
-def test_qk_norm_rope_append(ops, dtype, nh, nkv, d, rot):
+@pytest.mark.parametrize("nh,nkv,d,rot", [(4, 2, 16, 16), (6, 2, 32, 32), (5, 5, 48, 48), (8, 1, 128, 64), (3, 3, 80, 80),
+                                        (8, 2, 128, 128), (2, 1, 256, 256), (7, 3, 96, 96), (9, 3, 64, 64)])
+@pytest.mark.parametrize("lens,q_lens", [([70, 3, 129], [6, 3, 65]), ([300, 3, 200], [230, 3, 136])])
+def test_qk_norm_rope_append(ops, dtype, nh, nkv, d, rot, lens, q_lens):
+    # lens: lengths after the step; q_lens: tokens this step brings (the second sequence starts here);
+    # the longer step takes the 16-byte kernel where the sizes allow it
     torch.manual_seed(4)
-    lens = [70, 3, 129]                 # lengths after the step
-    q_lens = [6, 3, 65]                 # tokens this step brings (the second sequence starts here)
     ps = PagedSetup(lens, nkv, d, dtype, seed=4)
     N = sum(q_lens)
     ld = (nh + 2 * nkv) * d + 16        # row stride larger than the row
@@ -144,14 +146,14 @@ def test_qk_norm_rope_append(ops, dtype, nh, nkv, d, rot):
     before = qkv.clone()
     qw = 1 + 0.2 * torch.randn(d, device=DEV)
     kw = 1 + 0.2 * torch.randn(d, device=DEV)
-    eps, theta, max_pos = 1e-5, 1e4, 256
+    eps, theta, max_pos = 1e-5, 1e4, 512
     inv = plain.rope_inv_freq(rot, theta)
     ang = torch.outer(torch.arange(max_pos, dtype=torch.float32), inv)
     cos, sin = torch.cos(ang).to(DEV), torch.sin(ang).to(DEV)
     token_seq = torch.tensor(sum(([b] * n for b, n in enumerate(q_lens)), []), dtype=torch.int32, device=DEV)
     pos_list = sum(([lens[b] - q_lens[b] + i for i in range(q_lens[b])] for b in range(3)), [])
     token_pos = torch.tensor(pos_list, dtype=torch.int32, device=DEV)
-    qstart = torch.tensor([0, 6, 9, 74], dtype=torch.int32, device=DEV)
+    qstart = torch.tensor([0, q_lens[0], q_lens[0] + q_lens[1], N], dtype=torch.int32, device=DEV)
     k_before, v_before = ps.k_pages.clone(), ps.v_pages.clone()
     st = _status()
     ops.qk_norm_rope_append(qkv[:, : ld], N, nh, nkv, d, qw, kw, eps, cos, sin, rot, token_seq, token_pos, ps.seq_slot,
