@@ -1,5 +1,6 @@
-"""Each part alone against its plain formula, and a toy architecture whose mixer keeps state of its
-own: registered, built and stepped from the test, with no change to the package's files."""
+"""Each part alone against its plain formula, and toy architectures whose parts are defined here (a
+mixer that keeps state of its own, a feed-forward with routing, another position encoding):
+registered, built and stepped from the test, with no change to the package's files."""
 import math
 from dataclasses import dataclass
 
@@ -343,3 +344,169 @@ def test_order_is_data_a_block_twice_and_a_shared_cache(pe):
         assert rel_err(torch.cat(lg), ref[[0, 5, 6, 7, 8]]) < 1e-5
     finally:
         pe.config.unregister_architecture("LoopedQwen3")
+
+
+# ---- a toy feed-forward with routing and a toy position encoding ---------------------------------------
+@dataclass(frozen=True)
+class ToyMixConfig:
+    hidden_size: int = 40
+    vocab_size: int = 83
+    heads: int = 5
+    kv_heads: int = 1
+    head_dim: int = 16
+    experts: int = 3
+    expert_size: int = 24
+    slow_factor: float = 4.0
+    max_position_embeddings: int = 128
+    architecture: str = "ToyRoutedLM"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(**{k: v for k, v in d.items() if k != "architectures"})
+
+    def to_dict(self):
+        out = {k: getattr(self, k) for k in self.__dataclass_fields__ if k != "architecture"}
+        out["architectures"] = [self.architecture]
+        return out
+
+    max_positions = property(lambda self: self.max_position_embeddings)
+    stop_token_ids = ()
+    bos_token = 0
+
+
+class TopOneExperts:
+    """Every token goes to the expert with the largest router logit; its SwiGLU output is scaled by
+    that expert's softmax probability.  Router logits and probabilities in float32."""
+
+    graph_safe = False   # the routing is read on the host
+
+    @classmethod
+    def weight_decls(cls, params):
+        from importlib import import_module
+        WeightDecl = import_module("pytorch-engine_b200").parts.WeightDecl
+        h, e, i = params["hidden"], params["experts"], params["expert_size"]
+        decls = {"router": WeightDecl((e, h))}
+        for x in range(e):
+            decls.update({f"gate{x}": WeightDecl((i, h)), f"up{x}": WeightDecl((i, h)), f"down{x}": WeightDecl((h, i))})
+        return decls
+
+    def __init__(self, params, weights, runtime):
+        self.rt, self.n = runtime, int(params["experts"])
+        self.router = runtime.adopt(weights["router"], torch.float32)
+        self.w = [{k: runtime.adopt(weights[f"{k}{x}"]) for k in ("gate", "up", "down")} for x in range(self.n)]
+
+    def forward(self, x, ctx):
+        prob = torch.softmax(x.float() @ self.router.T, -1)
+        top_p, top_e = prob.max(-1)
+        out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+        for e in range(self.n):
+            rows = (top_e == e).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            xe = x[rows].contiguous()
+            g, u = self.rt.linear(xe, self.w[e]["gate"]).float(), self.rt.linear(xe, self.w[e]["up"]).float()
+            act = (g / (1 + torch.exp(-g)) * u).to(x.dtype)
+            out[rows] = self.rt.linear(act, self.w[e]["down"]).float() * top_p[rows, None]
+        return out.to(x.dtype)
+
+
+class SlowRotaryPosition:
+    """Rotary tables whose angles advance ``factor`` times slower (position / factor)."""
+
+    graph_safe = True
+    fusable_rotary = True
+
+    @classmethod
+    def weight_decls(cls, params):
+        return {}
+
+    def __init__(self, params, weights, runtime):
+        self.rotary_dim = int(params["rotary_dim"])
+        inv = plain.rope_inv_freq(self.rotary_dim, float(params["theta"]))
+        pos = torch.arange(int(params["max_positions"]), dtype=torch.float32) / float(params["factor"])
+        ang = torch.outer(pos, inv)
+        self.cos, self.sin = torch.cos(ang).to(runtime.device), torch.sin(ang).to(runtime.device)
+
+    def tables(self):
+        return self.cos, self.sin, self.rotary_dim
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding(pe):
+    """Parts defined here are registered, chosen layer by layer next to the package's own, built and
+    stepped: layer 0 has the slow rotary encoding and routed experts, layer 1 the usual ones."""
+    P, B, R = pe.parts.PartSpec, pe.parts.BlockSpec, pe.parts.RunStep
+    eps, theta = 1e-5, 500.0
+
+    def plan(cfg):
+        h, d = cfg.hidden_size, cfg.head_dim
+        norm = lambda n: P("rmsnorm", {"dim": h, "eps": eps}, {"weight": n})
+        att = lambda i, position: P("attention", {"hidden": h, "n_heads": cfg.heads, "n_kv_heads": cfg.kv_heads, "head_dim": d,
+                                                  "qk_norm": False, "eps": eps, "scale": None, "window": None,
+                                                  "position": position},
+                                    {k: f"l{i}.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj")})
+        routed = P("top_one_experts", {"hidden": h, "experts": cfg.experts, "expert_size": cfg.expert_size},
+                   {"router": "l0.router", **{f"{k}{x}": f"l0.{k}{x}" for x in range(cfg.experts) for k in ("gate", "up", "down")}})
+        dense = P("swiglu", {"hidden": h, "intermediate": 2 * h}, {"gate_proj": "l1.g", "up_proj": "l1.u", "down_proj": "l1.d"})
+        blocks = (B("pre_norm", norm("l0.n1"), att(0, "slow"), norm("l0.n2"), routed, name="routed"),
+                  B("pre_norm", norm("l1.n1"), att(1, "rope"), norm("l1.n2"), dense, name="dense"))
+        return pe.parts.ModelPlan(
+            hidden_size=h, vocab_size=cfg.vocab_size, max_positions=cfg.max_position_embeddings,
+            embedding=P("token_embedding", {"vocab": cfg.vocab_size, "hidden": h}, {"weight": "emb"}),
+            blocks=blocks, order=(R(0), R(1)), final_norm=norm("fn"),
+            head=P("linear_head", {"vocab": cfg.vocab_size, "hidden": h}, {"weight": "head"}),
+            positions={"rope": P("rope", {"rotary_dim": d, "theta": theta, "max_positions": cfg.max_position_embeddings}),
+                       "slow": P("slow_rope", {"rotary_dim": d, "theta": theta, "factor": cfg.slow_factor,
+                                               "max_positions": cfg.max_position_embeddings})})
+
+    pe.parts.register("feed_forward", "top_one_experts", TopOneExperts, replace=True)
+    pe.parts.register("position", "slow_rope", SlowRotaryPosition, replace=True)
+    pe.register_architecture("ToyRoutedLM", ToyMixConfig, plan, replace=True)
+    try:
+        cfg = ToyMixConfig()
+        eng = pe.Engine.from_random(cfg, seed=11, dtype="float32", max_cache_tokens=256, max_batch=2)
+        w = {k: v.float().cpu() for k, v in pe.weights.random_weights(eng.plan, 11, device=DEV).items()}
+        nH, nKV, d, h = cfg.heads, cfg.kv_heads, cfg.head_dim, cfg.hidden_size
+
+        def attention(x, i, factor):
+            S = x.shape[0]
+            pos = torch.arange(S, dtype=torch.float32) / factor
+            ang = torch.outer(pos, plain.rope_inv_freq(d, theta))
+            cos, sin = torch.cos(ang), torch.sin(ang)
+            q = plain.rope_rotate_neox((x @ w[f"l{i}.q_proj"].T).view(S, nH, d), cos, sin, d)
+            k = plain.rope_rotate_neox((x @ w[f"l{i}.k_proj"].T).view(S, nKV, d), cos, sin, d)
+            v = (x @ w[f"l{i}.v_proj"].T).view(S, nKV, d)
+            return plain.causal_gqa_attention(q, k, v, d ** -0.5).reshape(S, nH * d) @ w[f"l{i}.o_proj"].T
+
+        def plain_toy(tokens):
+            x = w["emb"][tokens]
+            x = x + attention(plain.rms_norm(x, w["l0.n1"], eps), 0, cfg.slow_factor)
+            n = plain.rms_norm(x, w["l0.n2"], eps)
+            prob = torch.softmax(n @ w["l0.router"].T, -1)
+            rows, chosen = [], []
+            for t in range(len(tokens)):
+                e = int(prob[t].argmax())
+                chosen.append(e)
+                rows.append(prob[t, e] * plain.swiglu(n[t:t + 1], w[f"l0.gate{e}"], w[f"l0.up{e}"], w[f"l0.down{e}"])[0])
+            x = x + torch.stack(rows)
+            x = x + attention(plain.rms_norm(x, w["l1.n1"], eps), 1, 1.0)
+            x = x + plain.swiglu(plain.rms_norm(x, w["l1.n2"], eps), w["l1.g"], w["l1.u"], w["l1.d"])
+            return plain.rms_norm(x, w["fn"], eps) @ w["head"].T, chosen
+
+        seqs = [[5, 9, 2, 77, 31, 8, 8, 40, 3, 61], [82, 0, 3, 3, 14, 7]]
+        refs = [plain_toy(s) for s in seqs]
+        assert len({e for _, ch in refs for e in ch}) > 1          # more than one expert is in use
+        slots = [eng.alloc_slot(), eng.alloc_slot()]
+        got = [[], []]
+        lg = eng.step([pe.StepEntry(slots[0], seqs[0][:6], (0, 5)), pe.StepEntry(slots[1], seqs[1][:2], (1,))])
+        got[0] += [lg[0].cpu(), lg[1].cpu()]; got[1].append(lg[2].cpu())
+        for k in range(4):
+            lg = eng.step([pe.StepEntry(slots[0], [seqs[0][6 + k]], (0,)), pe.StepEntry(slots[1], [seqs[1][2 + k]], (0,))])
+            got[0].append(lg[0].cpu()); got[1].append(lg[1].cpu())
+        for s in slots:
+            eng.free_slot(s)
+        assert rel_err(torch.stack(got[0]), refs[0][0][[0, 5, 6, 7, 8, 9]]) < 1e-5
+        assert rel_err(torch.stack(got[1]), refs[1][0][[1, 2, 3, 4, 5]]) < 1e-5
+    finally:
+        pe.parts.unregister("feed_forward", "top_one_experts")
+        pe.parts.unregister("position", "slow_rope")
+        pe.config.unregister_architecture("ToyRoutedLM")
