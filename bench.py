@@ -240,7 +240,7 @@ def main():
     if not args.no_prefill:
         T = args.prefill_tokens
         times = []
-        for it in range(4):
+        for it in range(7):   # the first is warm-up
             s = engine.alloc_slot()
             toks = torch.randint(0, vocab, (T,), generator=gen).tolist()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -222,6 +222,21 @@ def gemm_umma(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, status: 
     _count(1)
 
 
+def gemm_umma2(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, status: torch.Tensor, pair_offset: int = 0) -> None:
+    """``gemm_umma`` with two SMs per 256 x 256 output tile (csrc/gemm_umma2.cu, tcgen05 cta_group::2)."""
+    _need(gemm_umma_supported(x, weight, pair_offset), "gemm_umma2: needs bfloat16, K % 8 == 0, dense weight rows")
+    _need(out.stride(-1) == 1 and out.dtype in (torch.bfloat16, torch.float32), "gemm_umma2: out bfloat16 or float32")
+    m, k = x.shape
+    n = out.shape[1]
+    _need(weight.shape[1] == k and weight.shape[0] == (2 * n if pair_offset else n) and out.shape[0] == m,
+          "gemm_umma2: shapes do not match")
+    _need(not pair_offset or out.dtype == torch.bfloat16, "gemm_umma2: the fused gate writes bfloat16")
+    check(library().pe_gemm_umma2(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), out.stride(0), m, n, k,
+                                  1 if out.dtype == torch.float32 else 0, pair_offset, sm_count(x.device), _ptr(status),
+                                  _stream()), "gemm_umma2")
+    _count(1)
+
+
 def attention_umma_supported(dtype: torch.dtype, head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
     """Whether the tcgen05 prefill attention (csrc/attention_umma.cu) takes this shape."""
     return dtype == torch.bfloat16 and bool(library().pe_attention_umma_supported(head_dim, n_heads, n_kv_heads))

@@ -74,6 +74,7 @@ class Runtime:
         # refuses, the library product stands (measured: with fewer rows too few tiles exist to fill the SMs)
         self.own_large_gemm = True
         self.large_gemm_rows = 1024
+        self.pair_gemm = True       # large products on tcgen05 cta_group::2
 
     # ---- weights -------------------------------------------------------------------------
     def adopt(self, tensor: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -150,7 +151,9 @@ class Runtime:
         if self.takes_large_gemm(x, weight):
             if out is None:
                 out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
-            ops.gemm_umma(x, weight, out, self.status)
+            # two SMs per 256 x 256 tile (csrc/gemm_umma2.cu): measured 3-6 % faster than one SM per
+            # 128 x 256 tile on the plain products; the fused gate|up product stays on gemm_umma.cu
+            (ops.gemm_umma2 if self.pair_gemm else ops.gemm_umma)(x, weight, out, self.status)
             return out
         if self.takes_small_gemm(x, weight):
             # a handful of rows: the package's weight-streaming kernel (csrc/gemm_smallm.cu)

@@ -478,27 +478,30 @@ def test_gemm_smallm_refuses_what_it_does_not_take(pe, ops):
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 16, 8), (300, 515, 200), (2048, 1024, 512), (129, 257, 72),
                                    (640, 4096, 1024), (77, 1000, 4096)])
-def test_gemm_umma(ops, M, N, K):
+@pytest.mark.parametrize("kernel", ["gemm_umma", "gemm_umma2"])
+def test_gemm_umma(ops, M, N, K, kernel):
+    gemm = getattr(ops, kernel)    # one SM per 128 x 256 tile, or a pair of SMs per 256 x 256 tile
     torch.manual_seed(30)
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     w = (torch.randn(N, K, device=DEV) * 0.5).to(torch.bfloat16)
     want = x.float().cpu() @ w.float().cpu().T
     st = _status()
     out32 = torch.full((M, N), float("nan"), device=DEV)
-    ops.gemm_umma(x, w, out32, st)
+    gemm(x, w, out32, st)
     assert st.tolist()[0] == 0
     assert rel_err(out32.cpu(), want) < 2e-5
     out16 = torch.zeros(M, N + 8, device=DEV, dtype=torch.bfloat16)[:, :N]
-    ops.gemm_umma(x, w, out16, st)
+    gemm(x, w, out16, st)
     assert rel_err(out16.float().cpu(), want) < KTOL[torch.bfloat16]
     wide = torch.randn(M, K + 24, device=DEV).to(torch.bfloat16)
-    ops.gemm_umma(wide[:, :K], w, out32, st)
+    gemm(wide[:, :K], w, out32, st)
     assert rel_err(out32.cpu(), wide[:, :K].float().cpu() @ w.float().cpu().T) < 2e-5
     assert st.tolist()[0] == 0
 
 
 @pytest.mark.parametrize("M,I,K", [(128, 128, 64), (200, 384, 200), (1000, 1280, 1024), (5, 256, 4096)])
-def test_gemm_umma_with_the_gate_fused(ops, M, I, K):
+@pytest.mark.parametrize("kernel", ["gemm_umma", "gemm_umma2"])
+def test_gemm_umma_with_the_gate_fused(ops, M, I, K, kernel):
     torch.manual_seed(31)
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     w = (torch.randn(2 * I, K, device=DEV) * (2.0 / K ** 0.5)).to(torch.bfloat16)
@@ -507,7 +510,7 @@ def test_gemm_umma_with_the_gate_fused(ops, M, I, K):
     want = g / (1 + torch.exp(-g)) * u
     out = torch.zeros(M, I, device=DEV, dtype=torch.bfloat16)
     st = _status()
-    ops.gemm_umma(x, w, out, st, pair_offset=I)
+    getattr(ops, kernel)(x, w, out, st, pair_offset=I)
     assert st.tolist()[0] == 0
     assert rel_err(out.float().cpu(), want) < KTOL[torch.bfloat16]
 
