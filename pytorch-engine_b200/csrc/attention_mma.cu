@@ -368,6 +368,15 @@ __device__ __forceinline__ void decode_fold_page(uint32_t ks_base, uint32_t vs_b
 }
 
 // ---- decode ------------------------------------------------------------------------------------------
+// Keys per range of a sequence of `len` keys: the fixed split_keys, or (split_keys == 0) the
+// sequence's own length shared out evenly over max_splits ranges, in whole pages.  With even shares
+// a grid sized for the longest possible sequence keeps all its blocks busy on shorter ones.
+__device__ __forceinline__ int range_keys(const Args& a, int len) {
+  if (a.split_keys > 0) return a.split_keys;
+  const int per = (len + a.max_splits - 1) / a.max_splits;
+  return max(BN, (per + BN - 1) / BN * BN);
+}
+
 // grid: (max_splits, n_kv_heads, n_seqs); block: 128 threads; STAGES pages in flight.
 template <int HD, int STAGES>
 __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_constant__ CUtensorMap kmap,
@@ -388,7 +397,8 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
   const int group = a.group;
   const int tq = a.seq_qstart[b];
   const int len = a.seq_past[b] + 1;
-  const int k_lo = split * a.split_keys, k_hi = min(len, k_lo + a.split_keys);
+  const int per_range = range_keys(a, len);
+  const int k_lo = split * per_range, k_hi = min(len, k_lo + per_range);
   if (k_lo >= len) return;
   const int win_lo = a.window > 0 ? max(0, len - a.window) : 0;
   if (k_hi <= win_lo) return;
@@ -492,9 +502,10 @@ __global__ void decode_merge_kernel(Args a) {
   const int b = blockIdx.y, h = blockIdx.x;
   const int tq = a.seq_qstart[b];
   const int len = a.seq_past[b] + 1;
-  const int n_splits = (len + a.split_keys - 1) / a.split_keys;
+  const int per_range = range_keys(a, len);
+  const int n_splits = (len + per_range - 1) / per_range;
   const int win_lo = a.window > 0 ? max(0, len - a.window) : 0;
-  const int first = win_lo / a.split_keys;
+  const int first = win_lo / per_range;
   const size_t base = ((size_t)b * a.n_heads + h) * a.max_splits;
   float mx = -INFINITY;
   for (int s = first; s < n_splits; ++s) mx = fmaxf(mx, a.part_lse[base + s]);
@@ -571,6 +582,15 @@ static int launch(const Args& a, bool decode, int n_seqs, int max_q, cudaStream_
 }  // namespace fa
 }  // namespace pe
 
+// Decode blocks that one SM holds at a time (shared memory bound): the caller sizes the number of
+// ranges per sequence so that one wave of blocks covers the batch.
+extern "C" int pe_attention_mma_decode_blocks_per_sm(int head_dim) {
+  const size_t stage = 2 * (size_t)pe::fa::BN * head_dim * 2;
+  const size_t smem = 3 * stage + 16 * (size_t)head_dim * 2 + 1024 + 1024;   // + the block's static and reserved part
+  const int n = (int)((227 * 1024) / smem);
+  return n < 1 ? 1 : n;
+}
+
 // 1 if this file's kernels take the shape (bfloat16 only), else 0: the caller then uses the generic path.
 extern "C" int pe_attention_mma_supported(int head_dim, int n_heads, int n_kv_heads) {
   if (head_dim != 64 && head_dim != 128) return 0;
@@ -598,7 +618,7 @@ extern "C" int pe_attention_mma(int decode, const void* q, long long q_ld, void*
   a.k_pages = (const __nv_bfloat16*)k_pages; a.v_pages = (const __nv_bfloat16*)v_pages; a.status = status;
   a.part_acc = nullptr; a.part_lse = nullptr; a.split_keys = 0; a.max_splits = 0;
   if (decode) {
-    if (!scratch || split_keys <= 0 || split_keys % pe::fa::BN || max_splits <= 0) return PE_ERR_BAD_ARGUMENT;
+    if (!scratch || split_keys < 0 || split_keys % pe::fa::BN || max_splits <= 0) return PE_ERR_BAD_ARGUMENT;
     a.split_keys = split_keys; a.max_splits = max_splits;
     a.part_acc = scratch;
     a.part_lse = scratch + (size_t)n_seqs * n_heads * max_splits * head_dim;

@@ -237,6 +237,23 @@ def gemm_umma2(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, status:
     _count(1)
 
 
+def attention_mma_decode_ranges(device: torch.device, head_dim: int, n_seqs: int, n_kv_heads: int, max_kv_len: int,
+                                split_keys: int) -> tuple:
+    """(split_keys, max_splits) for the tensor-core decode attention.  When one wave of blocks can
+    hold at least two ranges per (sequence, kv head), each sequence's keys are shared out evenly
+    (split_keys 0) over that many ranges, but not over more than ranges of ``split_keys`` keys would
+    give (measured: the blocks of a second, partly filled wave cost more than longer ranges do, and
+    more, shorter ranges only add merge work).  Otherwise ranges of ``split_keys`` keys give several
+    waves anyway."""
+    slots = sm_count(device) * int(library().pe_attention_mma_decode_blocks_per_sm(head_dim))
+    pairs = max(1, n_seqs * n_kv_heads)
+    fixed = max(1, -(-max_kv_len // split_keys))
+    per_pair = slots // pairs
+    if per_pair < 2:
+        return split_keys, fixed
+    return 0, min(per_pair, fixed)
+
+
 def attention_umma_supported(dtype: torch.dtype, head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
     """Whether the tcgen05 prefill attention (csrc/attention_umma.cu) takes this shape."""
     return dtype == torch.bfloat16 and bool(library().pe_attention_umma_supported(head_dim, n_heads, n_kv_heads))

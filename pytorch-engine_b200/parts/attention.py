@@ -118,7 +118,11 @@ class GQAttention:
         max_splits = 0
         split_keys = SPLIT_KEYS
         if ctx.decode:
-            max_splits = ctx.max_splits(split_keys)
+            if self.use_mma:
+                split_keys, max_splits = ops.attention_mma_decode_ranges(
+                    q.device, self.head_dim, ctx.n_seqs, self.n_kv_heads, ctx.max_kv_len, SPLIT_KEYS)
+            else:
+                max_splits = ctx.max_splits(split_keys)
             scratch = ctx.buffer(
                 "attn.scratch",
                 (ops.attention_generic_scratch_floats(ctx.n_seqs, self.n_heads, self.head_dim, max_splits),),

@@ -378,7 +378,8 @@ def test_attention_umma_prefill_rescales_when_the_maximum_grows(ops):
 
 @pytest.mark.parametrize("nh,nkv,d", MMA_SHAPES)
 @pytest.mark.parametrize("window", [0, 300])
-def test_attention_mma_decode(ops, nh, nkv, d, window):
+@pytest.mark.parametrize("split_keys,max_splits", [(256, 5), (0, 5), (0, 1), (0, 23)])   # 0: even shares of each length
+def test_attention_mma_decode(ops, nh, nkv, d, window, split_keys, max_splits):
     torch.manual_seed(16)
     dtype = torch.bfloat16
     lens = [1, 700, 256, 257, 33, 64, 65, 513]
@@ -391,7 +392,6 @@ def test_attention_mma_decode(ops, nh, nkv, d, window):
     qstart = torch.arange(B + 1, dtype=torch.int32, device=DEV)
     past_t = torch.tensor(pasts, dtype=torch.int32, device=DEV)
     scale = 1 / math.sqrt(d)
-    split_keys, max_splits = 256, 5
     scratch = torch.full((ops.attention_generic_scratch_floats(B, nh, d, max_splits),), float("nan"), device=DEV)
     st = _status()
     ops.attention_mma(True, q_all, out, B, 1, nh, nkv, d, scale, window, qstart, past_t, ps.seq_slot, ps.table,
