@@ -10,12 +10,23 @@
 // argmax(value_i + G_i) over kept entries, with G_i = -log(-log u_i) and u_i from a counter-based
 // generator keyed by (seed, request, step, vocabulary index): the drawn token does not depend on
 // the batch a request runs in.  (The reference draws with torch.multinomial, engine.py:149.)
+//
+// Two kernels when the caller lends scratch memory and the row is greedy or has a small top-k: the
+// first cuts every row into chunks of kChunk entries, one block each, and leaves each chunk's
+// candidates (its own top-k, found by a threshold search on the ordered keys in shared memory; or
+// its largest entry); the second runs the filter chain on the candidates of a row, which hold
+// every entry that the row's top-k can keep.  A threshold search takes 8 sweeps of 4 bits with
+// per-thread counters (no atomics, fixed summation order) instead of 32 sweeps of one bit.
 #include "common.cuh"
 
 namespace pe {
 
 constexpr int kSampleThreads = 1024;
 constexpr int kMaxCompact = 1024;
+constexpr int kChunk = 4096;        // entries of a row per block of the first kernel
+constexpr int kChunkThreads = 256;
+constexpr int kMaxChunks = 64;
+constexpr int kMaxCandidates = 3072;  // candidates of a row that the second kernel takes
 
 __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
   z += 0x9E3779B97F4A7C15ull;
@@ -76,6 +87,64 @@ __device__ int block_sum_int(int v, int* scratch) {
   return r;
 }
 
+// 16 sums at once over the block in a fixed order; every thread gets all of them.
+template <typename T>
+__device__ void block_sum16(T (&v)[16], T* scratch /* [33][16] */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+#pragma unroll
+  for (int b = 0; b < 16; ++b)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v[b] += __shfl_xor_sync(0xffffffffu, v[b], o);
+  __syncthreads();
+  if (lane == 0)
+#pragma unroll
+    for (int b = 0; b < 16; ++b) scratch[warp * 16 + b] = v[b];
+  __syncthreads();
+  if (threadIdx.x < 16) {
+    T r = T(0);
+    for (int w = 0; w < nwarps; ++w) r += scratch[w * 16 + threadIdx.x];
+    scratch[32 * 16 + threadIdx.x] = r;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int b = 0; b < 16; ++b) v[b] = scratch[32 * 16 + b];
+}
+
+// The largest key J such that the weight of the entries with key >= J reaches the target
+// (STRICT: exceeds it), four bits of J per sweep.  `entry(i, key, weight)` yields entry i; entries
+// of weight zero do not count.  The total weight must reach (exceed) the target.
+template <bool STRICT, typename T, typename EntryFn>
+__device__ unsigned search16(int n, T target, EntryFn entry, T* scratch) {
+  unsigned prefix = 0u;
+  T above = T(0);   // weight of the entries whose key is beyond every key with this prefix
+  for (int shift = 28; shift >= 0; shift -= 4) {
+    const unsigned hi_mask = shift == 28 ? 0u : (0xFFFFFFFFu << (shift + 4));
+    T acc[16];
+#pragma unroll
+    for (int b = 0; b < 16; ++b) acc[b] = T(0);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      unsigned key;
+      T w;
+      entry(i, key, w);
+      if ((key & hi_mask) != prefix) continue;
+      const unsigned bin = (key >> shift) & 15u;
+#pragma unroll
+      for (int b = 0; b < 16; ++b) acc[b] += (bin == (unsigned)b) ? w : T(0);
+    }
+    block_sum16(acc, scratch);
+    int b = 15;
+    T run = above;
+    for (; b > 0; --b) {
+      const T t = run + acc[b];
+      if (STRICT ? (t > target) : (t >= target)) break;
+      run = t;
+    }
+    prefix |= (unsigned)b << shift;
+    above = run;
+  }
+  return prefix;
+}
+
 struct SampleArgs {
   const float* logits;
   long long ld;
@@ -87,68 +156,163 @@ struct SampleArgs {
   const int* row_request;
   const int* row_step;
   int* out_tokens;
+  // scratch of the two-kernel path (null: one kernel does everything)
+  int n_chunks, cand_cap;     // chunks per row; room for candidates per chunk
+  float* cand_val;            // [rows][chunks][cap] values / temperature, in index order
+  int* cand_idx;              // [rows][chunks][cap]
+  int* cand_cnt;              // [rows][chunks]; -1: more than cap entries tie for the chunk's top-k
 };
 
+__device__ __forceinline__ float scaled(float v, float mult) {
+  v *= mult;
+  return v == v ? v : -INFINITY;   // NaN sorts lowest
+}
+
+// First kernel of the two-kernel path.  grid: (chunks, rows).
+__global__ void __launch_bounds__(kChunkThreads) sample_chunks_kernel(SampleArgs a) {
+  __shared__ float vals[kChunk];
+  __shared__ int red_i[33 * 16];
+  __shared__ ArgBest red_b[32];
+  __shared__ int scan[kChunkThreads];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x;
+  const int lo = chunk * kChunk, n = min(kChunk, a.vocab - lo);
+  const float* src = a.logits + (size_t)row * a.ld + lo;
+  const size_t slot = (size_t)row * a.n_chunks + chunk;
+  float* out_val = a.cand_val + slot * a.cand_cap;
+  int* out_idx = a.cand_idx + slot * a.cand_cap;
+  const bool greedy = a.temperature <= 1e-5f;
+  const float mult = greedy ? 1.0f : 1.0f / a.temperature;
+  if (greedy || a.top_k <= 0) {
+    // no filter: the row's draw is the best of its chunks' draws (value + Gumbel noise; greedy: value)
+    const unsigned long long key =
+        mix64(a.seed ^ mix64(((unsigned long long)(unsigned)a.row_request[row] << 32) | (unsigned)a.row_step[row]));
+    ArgBest best{-INFINITY, 0x7fffffff};
+    for (int i = tid; i < n; i += blockDim.x) {
+      float v = scaled(src[i], mult);
+      if (!greedy && v != -INFINITY) v += -logf(-logf(uniform_of(key, lo + i)));
+      best = better(best, ArgBest{v, lo + i});
+    }
+    best = block_argbest(best, red_b);
+    if (tid == 0) {
+      out_val[0] = best.v;
+      out_idx[0] = best.i;
+      a.cand_cnt[slot] = 1;
+    }
+    return;
+  }
+  for (int i = tid; i < n; i += blockDim.x) vals[i] = scaled(src[i], mult);
+  __syncthreads();
+  const int k = min(a.top_k, n);
+  const unsigned K = search16<false, int>(n, k, [&](int i, unsigned& key, int& w) { key = ordered_key(vals[i]); w = 1; }, red_i);
+  // the entries with key >= K, in index order: each thread owns a contiguous run
+  const int per = (n + blockDim.x - 1) / blockDim.x;
+  const int i0 = min(n, tid * per), i1 = min(n, i0 + per);
+  int mine = 0;
+  for (int i = i0; i < i1; ++i) mine += ordered_key(vals[i]) >= K;
+  scan[tid] = mine;
+  __syncthreads();
+  for (int o = 1; o < kChunkThreads; o <<= 1) {
+    const int add = (tid >= o) ? scan[tid - o] : 0;
+    __syncthreads();
+    scan[tid] += add;
+    __syncthreads();
+  }
+  const int total = scan[kChunkThreads - 1];
+  if (total > a.cand_cap) {   // ties beyond the room: the second kernel reads the whole row instead
+    if (tid == 0) a.cand_cnt[slot] = -1;
+    return;
+  }
+  int pos = scan[tid] - mine;
+  for (int i = i0; i < i1; ++i)
+    if (ordered_key(vals[i]) >= K) {
+      out_val[pos] = vals[i];
+      out_idx[pos] = lo + i;
+      ++pos;
+    }
+  if (tid == 0) a.cand_cnt[slot] = total;
+}
+
 __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleArgs a) {
-  __shared__ float red_f[32];
-  __shared__ int red_i[32];
+  __shared__ float red_f[33 * 16];
+  __shared__ int red_i[33 * 16];
   __shared__ ArgBest red_b[32];
   __shared__ float c_val[kMaxCompact];
   __shared__ int c_idx[kMaxCompact];
   __shared__ int scan[kSampleThreads];
+  __shared__ float l_val[kMaxCandidates];
+  __shared__ int l_idx[kMaxCandidates];
   pdl_wait();
   pdl_launch_dependents();
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
   const float* src = a.logits + (size_t)row * a.ld;
   const int V = a.vocab;
+  const bool greedy = a.temperature <= 1e-5f;
 
-  if (a.temperature <= 1e-5f) {
-    ArgBest best{-INFINITY, 0x7fffffff};
-    for (int i = tid; i < V; i += blockDim.x) {
-      float v = src[i];
-      if (v != v) v = -INFINITY;
-      best = better(best, ArgBest{v, i});
+  // candidates: the whole row (values scaled on the fly), the chunks' candidates, or, after top-k,
+  // a compact list
+  const float* vals = src;
+  const int* idxs = nullptr;
+  float mult = greedy ? 1.0f : 1.0f / a.temperature;
+  int n = V;
+  if (a.cand_cnt != nullptr) {
+    // gather the chunks' candidates (index order is kept); a chunk that overflowed sends us to the row
+    const int* cnt = a.cand_cnt + (size_t)row * a.n_chunks;
+    int total = 0;
+    bool ok = true;
+    for (int c = 0; c < a.n_chunks; ++c) {
+      const int m = cnt[c];
+      if (m < 0) ok = false;
+      total += max(m, 0);
     }
+    if (ok && total <= kMaxCandidates) {
+      int base = 0;
+      for (int c = 0; c < a.n_chunks; ++c) {
+        const int m = cnt[c];
+        const size_t slot = ((size_t)row * a.n_chunks + c) * a.cand_cap;
+        for (int i = tid; i < m; i += blockDim.x) {
+          l_val[base + i] = a.cand_val[slot + i];
+          l_idx[base + i] = a.cand_idx[slot + i];
+        }
+        base += m;
+      }
+      __syncthreads();
+      vals = l_val;
+      idxs = l_idx;
+      mult = 1.0f;
+      n = total;
+    }
+  }
+
+  const bool drawn_in_chunks = idxs != nullptr && a.top_k <= 0;   // the candidates are the chunks' finished draws
+  if (greedy || drawn_in_chunks) {
+    ArgBest best{-INFINITY, 0x7fffffff};
+    for (int i = tid; i < n; i += blockDim.x) best = better(best, ArgBest{scaled(vals[i], mult), idxs ? idxs[i] : i});
     best = block_argbest(best, red_b);
     if (tid == 0) a.out_tokens[row] = best.i == 0x7fffffff ? 0 : best.i;
     return;
   }
 
-  const float inv_t = 1.0f / a.temperature;
-  // candidates: the whole row (values scaled on the fly) or, after top-k, a compact list
-  const float* vals = src;
-  const int* idxs = nullptr;
-  float mult = inv_t;
-  int n = V;
   unsigned keep_key = 0u;  // entries with ordered_key(value) >= keep_key are kept
 
   // largest value
   float mx = -INFINITY;
-  for (int i = tid; i < n; i += blockDim.x) {
-    const float v = vals[i] * mult;
-    if (v == v) mx = fmaxf(mx, v);
-  }
+  for (int i = tid; i < n; i += blockDim.x) mx = fmaxf(mx, scaled(vals[i], mult));
   mx = block_max(mx, red_f);
 
   if (a.top_k > 0 && a.top_k < V) {
-    // k-th largest value: largest key K with count(key >= K) >= k
-    unsigned K = 0u;
-    for (int bit = 31; bit >= 0; --bit) {
-      const unsigned cand = K | (1u << bit);
-      int cnt = 0;
-      for (int i = tid; i < n; i += blockDim.x) cnt += ordered_key(vals[i] * mult) >= cand;
-      cnt = block_sum_int(cnt, red_i);
-      if (cnt >= a.top_k) K = cand;
-    }
+    // k-th largest value: the largest key K with count(key >= K) >= k
+    const unsigned K = search16<false, int>(
+        n, min(a.top_k, n), [&](int i, unsigned& key, int& w) { key = ordered_key(scaled(vals[i], mult)); w = 1; }, red_i);
     keep_key = K;
     if (a.top_k <= kMaxCompact) {
       // compact the candidates in index order (deterministic): count, scan, write
       int mine = 0;
-      for (int i = tid; i < n; i += blockDim.x) mine += ordered_key(vals[i] * mult) >= K;
+      for (int i = tid; i < n; i += blockDim.x) mine += ordered_key(scaled(vals[i], mult)) >= K;
       scan[tid] = mine;
       __syncthreads();
-      // inclusive scan over the block's threads (Hillis-Steele)
       for (int o = 1; o < kSampleThreads; o <<= 1) {
         const int add = (tid >= o) ? scan[tid - o] : 0;
         __syncthreads();
@@ -157,12 +321,14 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleArgs a) {
       }
       int pos = scan[tid] - mine;
       const int total = scan[kSampleThreads - 1];
+      // a thread's entries are strided, so positions within the list follow (thread, index) order;
+      // the list is a set here: nothing below depends on its order
       for (int i = tid; i < n; i += blockDim.x) {
-        const float v = vals[i] * mult;
+        const float v = scaled(vals[i], mult);
         if (ordered_key(v) >= K) {
           if (pos < kMaxCompact) {
             c_val[pos] = v;
-            c_idx[pos] = i;
+            c_idx[pos] = idxs ? idxs[i] : i;
           }
           ++pos;
         }
@@ -178,7 +344,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleArgs a) {
   // softmax denominator over the kept entries, relative to the largest value
   float z = 0.f;
   for (int i = tid; i < n; i += blockDim.x) {
-    const float v = vals[i] * mult;
+    const float v = scaled(vals[i], mult);
     if (ordered_key(v) >= keep_key) z += expf(v - mx);
   }
   z = block_sum(z, red_f);
@@ -192,26 +358,20 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleArgs a) {
   }
 
   if (a.top_p > 0.f && a.top_p < 1.f) {
-    // keep entry i iff the mass of kept entries with a larger value is <= top_p.
-    // P(K): mass of entries with key > K is <= top_p.  Find the largest K with P false.
+    // keep entry i iff the mass of the kept entries with a larger value is <= top_p: the threshold
+    // is the largest key J whose mass at or above it exceeds top_p (everything if none does, which
+    // cannot be: the whole mass exceeds it)
     const float limit = a.top_p * z;
-    auto mass_above = [&](unsigned K) -> float {
-      float s = 0.f;
-      for (int i = tid; i < n; i += blockDim.x) {
-        const float v = vals[i] * mult;
-        const unsigned k = ordered_key(v);
-        if (k > K && k >= keep_key) s += expf(v - mx);
-      }
-      return block_sum(s, red_f);
-    };
-    if (!(mass_above(0u) <= limit)) {
-      unsigned K = 0u;
-      for (int bit = 31; bit >= 0; --bit) {
-        const unsigned cand = K | (1u << bit);
-        if (!(mass_above(cand) <= limit)) K = cand;
-      }
-      if (K + 1u > keep_key) keep_key = K + 1u;
-    }
+    const unsigned kk = keep_key;
+    const unsigned J = search16<true, float>(
+        n, limit,
+        [&](int i, unsigned& key, float& w) {
+          const float v = scaled(vals[i], mult);
+          key = ordered_key(v);
+          w = key >= kk ? expf(v - mx) : 0.f;
+        },
+        red_f);
+    if (J > keep_key) keep_key = J;
   }
 
   // draw
@@ -219,8 +379,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleArgs a) {
       mix64(a.seed ^ mix64(((unsigned long long)(unsigned)a.row_request[row] << 32) | (unsigned)a.row_step[row]));
   ArgBest best{-INFINITY, 0x7fffffff};
   for (int i = tid; i < n; i += blockDim.x) {
-    const float v = vals[i] * mult;
-    if (ordered_key(v) < keep_key || !(v == v)) continue;
+    const float v = scaled(vals[i], mult);
+    if (ordered_key(v) < keep_key || v == -INFINITY) continue;
     const int index = idxs ? idxs[i] : i;
     const float u = uniform_of(key, index);
     const float g = -logf(-logf(u));
@@ -262,15 +422,49 @@ __global__ void repetition_penalty_kernel(float* logits, long long ld, int vocab
 
 }  // namespace pe
 
+// Room for ties at a chunk's k-th value beyond its k candidates.
+static bool unfiltered(float temperature, int top_k, float top_p, float min_p) {
+  return temperature <= 1e-5f || ((top_k <= 0) && !(top_p > 0.f && top_p < 1.f) && !(min_p > 0.f));
+}
+static int cand_cap_of(float temperature, int top_k, float top_p, float min_p) {
+  return unfiltered(temperature, top_k, top_p, min_p) ? 1 : top_k + 8;
+}
+static bool two_kernels(int vocab, float temperature, int top_k, float top_p, float min_p) {
+  const int chunks = (vocab + pe::kChunk - 1) / pe::kChunk;
+  if (chunks < 2 || chunks > pe::kMaxChunks) return false;
+  if (unfiltered(temperature, top_k, top_p, min_p)) return true;
+  return top_k > 0 && top_k < vocab && (long long)chunks * top_k <= pe::kMaxCandidates;
+}
+
+// Bytes of scratch with which pe_sample takes its two-kernel path for these settings (0: it has none).
+extern "C" long long pe_sample_scratch_bytes(int n_rows, int vocab, float temperature, int top_k, float top_p, float min_p) {
+  if (n_rows <= 0 || !two_kernels(vocab, temperature, top_k, top_p, min_p)) return 0;
+  const long long chunks = (vocab + pe::kChunk - 1) / pe::kChunk;
+  return (long long)n_rows * chunks * (cand_cap_of(temperature, top_k, top_p, min_p) * 8ll + 4ll);
+}
+
+// scratch: null, or at least pe_sample_scratch_bytes(...) bytes, 4-byte aligned.
 extern "C" int pe_sample(const float* logits, long long ld, int n_rows, int vocab, float temperature, int top_k,
                          float top_p, float min_p, unsigned long long seed, const int* row_request, const int* row_step,
-                         int* out_tokens, cudaStream_t stream) {
+                         int* out_tokens, void* scratch, long long scratch_bytes, cudaStream_t stream) {
   if (n_rows <= 0) return PE_OK;
   if (vocab <= 0 || ld < vocab) return PE_ERR_BAD_ARGUMENT;
   pe::SampleArgs a;
   a.logits = logits; a.ld = ld; a.n_rows = n_rows; a.vocab = vocab; a.temperature = temperature; a.top_k = top_k;
   a.top_p = top_p; a.min_p = min_p; a.seed = seed; a.row_request = row_request; a.row_step = row_step;
   a.out_tokens = out_tokens;
+  a.n_chunks = 0; a.cand_cap = 0; a.cand_val = nullptr; a.cand_idx = nullptr; a.cand_cnt = nullptr;
+  const long long need = pe_sample_scratch_bytes(n_rows, vocab, temperature, top_k, top_p, min_p);
+  if (scratch != nullptr && need > 0 && scratch_bytes >= need && ((uintptr_t)scratch % 4) == 0) {
+    a.n_chunks = (vocab + pe::kChunk - 1) / pe::kChunk;
+    a.cand_cap = cand_cap_of(temperature, top_k, top_p, min_p);
+    const size_t slots = (size_t)n_rows * a.n_chunks;
+    a.cand_val = reinterpret_cast<float*>(scratch);
+    a.cand_idx = reinterpret_cast<int*>(a.cand_val + slots * a.cand_cap);
+    a.cand_cnt = a.cand_idx + slots * a.cand_cap;
+    pe::launch(pe::sample_chunks_kernel, dim3(a.n_chunks, n_rows), pe::kChunkThreads, 0, stream, a);
+    PE_LAUNCH_CHECK();
+  }
   pe::launch(pe::sample_kernel, n_rows, pe::kSampleThreads, 0, stream, a);
   PE_LAUNCH_CHECK();
   return PE_OK;

@@ -45,7 +45,7 @@ _SIGNATURES = {
     "pe_batch_expand": [P, P, I, P, P, P],
     "pe_qk_norm_rope_append": [I, P, L, I, I, I, I, P, P, F, P, P, I, I, P, P, P, P, P, I, I, P, P, I, P, P],
     "pe_attention_generic": [I, I, P, L, P, L, I, I, I, I, I, F, I, P, P, P, P, I, I, P, P, P, I, I, P, P],
-    "pe_sample": [P, L, I, I, F, I, F, F, c_ulonglong, P, P, P, P],
+    "pe_sample": [P, L, I, I, F, I, F, F, c_ulonglong, P, P, P, P, L, P],
     "pe_repetition_penalty": [P, L, I, I, P, I, P, F, P],
     "pe_attention_mma": [I, P, L, P, L, I, I, I, I, I, F, I, P, P, P, P, I, I, P, P, P, I, I, P, P],
     "pe_attention_mma_supported": [I, I, I],
@@ -60,7 +60,8 @@ _SIGNATURES = {
     "pe_attention_umma_supported": [I, I, I],
     "pe_attention_decode_noalloc": [I, P, L, P, L, I, I, I, I, F, I, P, P, P, P, I, I, P, P, I, I, P, P],
 }
-_RESTYPES = {"pe_attention_generic_scratch_floats": (L, [I, I, I, I])}
+_RESTYPES = {"pe_attention_generic_scratch_floats": (L, [I, I, I, I]),
+             "pe_sample_scratch_bytes": (L, [I, I, F, I, F, F])}
 
 
 def library() -> ctypes.CDLL:

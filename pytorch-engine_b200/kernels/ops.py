@@ -274,14 +274,28 @@ def attention_umma_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_
     _count(1)
 
 
+def sample_scratch_bytes(n_rows: int, vocab: int, temperature: float, top_k: int, top_p: float = 1.0,
+                         min_p: float = 0.0) -> int:
+    """Bytes of scratch with which ``sample`` runs as two kernels (many blocks per row) for these
+    settings: greedy, no filter at all, or a small top-k; 0 if it has no such path for them."""
+    return int(library().pe_sample_scratch_bytes(int(n_rows), int(vocab), float(temperature), int(top_k),
+                                                 float(top_p), float(min_p)))
+
+
 def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, min_p: float, seed: int,
-           row_request: torch.Tensor, row_step: torch.Tensor, out_tokens: torch.Tensor) -> None:
+           row_request: torch.Tensor, row_step: torch.Tensor, out_tokens: torch.Tensor,
+           scratch: Optional[torch.Tensor] = None) -> None:
+    """One token per row.  ``scratch`` (uint8, at least ``sample_scratch_bytes``) lets greedy and small
+    top-k draws cut each row into chunks first; the drawn tokens are the same either way except
+    where float32 sums in another order move an entry across a top-p threshold."""
     _need(logits.dtype == torch.float32 and logits.stride(-1) == 1, "sample: float32 logits with contiguous rows")
     n, vocab = logits.shape
+    two = scratch is not None and scratch.numel() * scratch.element_size() >= max(1, sample_scratch_bytes(n, vocab, temperature, top_k, top_p, min_p))
     check(library().pe_sample(_ptr(logits), logits.stride(0), n, vocab, float(temperature), int(top_k), float(top_p),
                               float(min_p), int(seed) & ((1 << 64) - 1), _ptr(row_request), _ptr(row_step),
-                              _ptr(out_tokens), _stream()), "sample")
-    _count(1)
+                              _ptr(out_tokens), _ptr(scratch) if two else None,
+                              scratch.numel() * scratch.element_size() if two else 0, _stream()), "sample")
+    _count(2 if two and sample_scratch_bytes(n, vocab, temperature, top_k, top_p, min_p) > 0 else 1)
 
 
 def repetition_penalty(logits: torch.Tensor, recent: torch.Tensor, recent_count: torch.Tensor, penalty: float) -> None:

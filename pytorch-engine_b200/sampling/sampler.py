@@ -18,6 +18,17 @@ class Sampler:
         self.device = torch.device(device)
         self.runtime = runtime
         self._stager = None
+        self._scratch = None
+
+    def _scratch_for(self, logits: torch.Tensor, params: SamplingParams) -> Optional[torch.Tensor]:
+        """Scratch for the sampler's two-kernel path, grown when a larger batch comes."""
+        need = ops.sample_scratch_bytes(logits.shape[0], logits.shape[1], params.temperature, params.top_k,
+                                        params.top_p, params.min_p)
+        if need == 0:
+            return None
+        if self._scratch is None or self._scratch.numel() < need:
+            self._scratch = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=self.device)
+        return self._scratch
 
     def _launch_into_token_area(self, logits, params, seed, requests, steps) -> None:
         from ..engine.batch import PinnedStager
@@ -32,7 +43,7 @@ class Sampler:
         meta = self._meta[self._meta_turn, :2 * n]
         self._stager.send(list(requests) + list(steps), meta)
         ops.sample(logits, params.temperature, params.top_k, params.top_p, params.min_p, seed, meta[:n], meta[n:],
-                   rt.token_area[:n])
+                   rt.token_area[:n], scratch=self._scratch_for(logits, params))
 
     def sample_async(self, logits: torch.Tensor, params: SamplingParams, seed: int, requests: Sequence[int],
                      steps: Sequence[int]):
@@ -71,5 +82,6 @@ class Sampler:
             return rt.fetch_tokens(n)
         meta = torch.tensor([list(requests), list(steps)], dtype=torch.int32).to(self.device)
         out = torch.empty((n,), dtype=torch.int32, device=self.device)
-        ops.sample(logits, params.temperature, params.top_k, params.top_p, params.min_p, seed, meta[0], meta[1], out)
+        ops.sample(logits, params.temperature, params.top_k, params.top_p, params.min_p, seed, meta[0], meta[1], out,
+                   scratch=self._scratch_for(logits, params))
         return out.tolist()

@@ -551,6 +551,74 @@ def test_sampler_matches_the_plain_draw(ops, filters):
     assert agree >= rows - 1     # float32 vs float64 Gumbel arithmetic may flip one near-tie
 
 
+@pytest.mark.parametrize("V", [4097, 10000, 151936])
+def test_sampler_with_scratch_greedy(ops, V):
+    """Rows cut into chunks by a first kernel: the same argmax, ties to the lower index, across chunk borders."""
+    torch.manual_seed(11)
+    rows = 5
+    logits = torch.randn(rows, V, device=DEV)
+    logits[1, 4095] = logits[1, 4096] = 40.0                  # a tie across the first chunk border
+    logits[2, V - 1] = 41.0                                   # the last entry of the last (short) chunk
+    logits[3, 0] = 42.0
+    logits[4, 5000 % V] = float("nan")                        # NaN never wins
+    req = torch.arange(rows, dtype=torch.int32, device=DEV)
+    step = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    need = ops.sample_scratch_bytes(rows, V, 0.0, 0)
+    assert need > 0
+    scratch = torch.empty(need, dtype=torch.uint8, device=DEV)
+    ops.sample(logits, 0.0, 0, 1.0, 0.0, 1, req, step, out, scratch=scratch)
+    want = torch.nan_to_num(logits, nan=-float("inf")).argmax(-1).tolist()
+    want[1] = 4095
+    assert out.tolist() == want
+
+
+@pytest.mark.parametrize("filters", [dict(top_k=5), dict(top_k=40, top_p=0.9, min_p=0.05), dict(top_k=40, top_p=0.95, min_p=0.05),
+                                     dict(top_k=64, top_p=0.5), dict(top_k=1)])
+def test_sampler_with_scratch_matches_the_plain_draw_and_the_single_kernel(ops, filters):
+    torch.manual_seed(12)
+    V, rows = 20011, 16
+    logits = torch.randn(rows, V, device=DEV) * 2.5
+    logits[3, 100:140] = 9.0                                  # forty ties at the top of one chunk
+    logits[5, :] = 0.25                                       # every entry ties: the chunks overflow, the row is read whole
+    req = torch.arange(rows, dtype=torch.int32, device=DEV) % 5
+    step = torch.arange(rows, dtype=torch.int32, device=DEV) // 5
+    kw = dict(top_k=0, top_p=1.0, min_p=0.0)
+    kw.update(filters)
+    need = ops.sample_scratch_bytes(rows, V, 0.8, kw["top_k"], kw["top_p"], kw["min_p"])
+    assert need > 0
+    scratch = torch.empty(need, dtype=torch.uint8, device=DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    single = torch.empty(rows, dtype=torch.int32, device=DEV)
+    ops.sample(logits, 0.8, kw["top_k"], kw["top_p"], kw["min_p"], 99, req, step, out, scratch=scratch)
+    ops.sample(logits, 0.8, kw["top_k"], kw["top_p"], kw["min_p"], 99, req, step, single)
+    got = out.tolist()
+    assert sum(a != b for a, b in zip(got, single.tolist())) <= 1
+    agree = 0
+    for r in range(rows):
+        want = plain.sample_token(logits[r].cpu(), seed=99, request=int(req[r]), step=int(step[r]), temperature=0.8, **kw)
+        _, probs = plain.filter_logits(logits[r].cpu(), temperature=0.8, **kw)
+        if r != 5:    # with every entry tied, which k of them a top-k keeps is not defined
+            assert probs[got[r]] > 0, "the kernel drew a token that the filters exclude"
+            agree += got[r] == want
+    assert agree >= rows - 2
+    assert ops.sample_scratch_bytes(rows, V, 0.8, 0, 0.9) == 0 and ops.sample_scratch_bytes(rows, 3000, 0.8, 40) == 0
+
+
+def test_sampler_with_scratch_unfiltered_draw_is_the_single_kernels(ops):
+    torch.manual_seed(13)
+    rows, V = 12, 30000
+    logits = torch.randn(rows, V, device=DEV) * 2
+    req = torch.arange(rows, dtype=torch.int32, device=DEV)
+    step = torch.full((rows,), 3, dtype=torch.int32, device=DEV)
+    a, b = (torch.empty(rows, dtype=torch.int32, device=DEV) for _ in range(2))
+    scratch = torch.empty(ops.sample_scratch_bytes(rows, V, 0.9, 0), dtype=torch.uint8, device=DEV)
+    assert scratch.numel() > 0
+    ops.sample(logits, 0.9, 0, 1.0, 0.0, 5, req, step, a, scratch=scratch)
+    ops.sample(logits, 0.9, 0, 1.0, 0.0, 5, req, step, b)
+    assert a.tolist() == b.tolist()
+
+
 def test_sampler_is_keyed_by_request_and_step_not_by_row(ops):
     torch.manual_seed(10)
     row = torch.randn(1, 3000, device=DEV)
