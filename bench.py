@@ -2,6 +2,7 @@
 """Benchmark: decode tokens/s of a Qwen3-8B-shaped model (random weights, bfloat16) on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --micro gemm|decode_attention|sampler     (single kernels, text output)
 
 A step is one decode step: every live sequence gets one token (model step + sampler).  The default
 run has the layer sizes of the Qwen3-8B shape, a batch of 8 and a context of 4,096.  One JSON line
@@ -136,6 +137,8 @@ def main():
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cuda-graph", action="store_true")
+    ap.add_argument("--micro", type=str, default=None,
+                    help="time single kernels at the preset's sizes instead (gemm, decode_attention, sampler) and print text")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -153,6 +156,13 @@ def main():
 
     pe = importlib.import_module("pytorch-engine_b200")
     ops = pe.kernels.ops
+    if args.micro:
+        micro = importlib.import_module("pytorch-engine_b200.kernels.microbench")
+        if args.micro not in micro.CASES:
+            print(f"bench.py: --micro takes one of {sorted(micro.CASES)}")
+            return 2
+        micro.CASES[args.micro](pe.preset(args.preset), "cuda:0")
+        return 0
     peaks = load_peaks()
     full = pe.preset(args.preset)
     layers_model = full.num_hidden_layers

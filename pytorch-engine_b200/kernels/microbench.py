@@ -1,0 +1,132 @@
+"""Timings of single kernels at the sizes of a configuration, printed as text (``bench.py --micro NAME``).
+
+Each case is timed with CUDA events on the launching stream after warm-up.  Cases that compare
+kernels call them in turn inside one loop, so that all see the same clocks, and flush L2 between
+calls by writing a 256 MB buffer (the matrix products, the decode attention) or time a run of calls
+in a row (the sampler, whose logits come out of the preceding kernel and sit in L2).
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, Dict, List, Sequence
+
+import torch
+
+from . import ops
+
+
+def _flush_buffer(device) -> torch.Tensor:
+    return torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+
+def time_in_turn(fns: Sequence[Callable[[], None]], flush: torch.Tensor, rounds: int = 15) -> List[float]:
+    """Median microseconds of each callable, called in turn ``rounds`` times with L2 flushed before each call."""
+    for f in fns:
+        for _ in range(2):
+            f()
+    times: List[List[float]] = [[] for _ in fns]
+    for _ in range(rounds):
+        for i, f in enumerate(fns):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            f()
+            b.record()
+            torch.cuda.synchronize()
+            times[i].append(a.elapsed_time(b) * 1e3)
+    return [sorted(t)[len(t) // 2] for t in times]
+
+
+def time_in_a_row(f: Callable[[], None], calls: int = 20) -> float:
+    """Microseconds per call over ``calls`` calls in a row."""
+    for _ in range(3):
+        f()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(calls):
+        f()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / calls * 1e3
+
+
+def gemm(cfg, device, rows: Sequence[int] = (2048, 4096, 1024)) -> None:
+    """The tcgen05 products (one SM per tile, a pair of SMs per tile) and the library product."""
+    status = torch.zeros(4, dtype=torch.int32, device=device)
+    flush = _flush_buffer(device)
+    h, i = cfg.hidden_size, cfg.intermediate_size
+    qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+    shapes = [("q|k|v", qkv, h, 0), ("o", h, cfg.num_attention_heads * cfg.head_dim, 0), ("gate|up fused", i, h, 1),
+              ("down", h, i, 0)]
+    for m in rows:
+        for name, n, k, pair in shapes:
+            x = torch.randn(m, k, device=device).to(torch.bfloat16)
+            w = torch.randn(2 * n if pair else n, k, device=device).to(torch.bfloat16)
+            out = torch.empty(m, n, device=device, dtype=torch.bfloat16)
+            flops = 2.0 * m * (2 * n if pair else n) * k
+            fns = [lambda: ops.gemm_umma(x, w, out, status, pair_offset=n if pair else 0),
+                   lambda: ops.gemm_umma2(x, w, out, status, pair_offset=n if pair else 0)]
+            if not pair:
+                fns.append(lambda: torch.mm(x, w.T))
+            t = time_in_turn(fns, flush)
+            line = (f"M={m} {name} N={n} K={k}: one SM per tile {t[0]:.0f} us ({flops / t[0] / 1e6:.0f} TFLOP/s)  "
+                    f"pair of SMs {t[1]:.0f} us ({flops / t[1] / 1e6:.0f} TFLOP/s)")
+            if len(t) > 2:
+                line += f"  library {t[2]:.0f} us ({flops / t[2] / 1e6:.0f} TFLOP/s)"
+            print(line, flush=True)
+    print("status word", status.tolist(), flush=True)
+
+
+def decode_attention(cfg, device, cases: Sequence[Sequence[int]] = ((8, 4090), (1, 4090), (16, 4090), (64, 4090))) -> None:
+    """Split + merge decode attention with ranges of 512 keys, the ranges the engine picks, and other even splits."""
+    nh, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    flush = _flush_buffer(device)
+    for batch, length in cases:
+        per = (length + 63) // 64 + 1
+        pages = batch * per
+        kp = (torch.randn(pages, nkv, 64, d, device=device) * 0.5).to(torch.bfloat16)
+        vp = (torch.randn(pages, nkv, 64, d, device=device) * 0.5).to(torch.bfloat16)
+        table = torch.arange(pages, dtype=torch.int32, device=device).view(batch, per)
+        q = torch.randn(batch, (nh + 2 * nkv) * d, device=device).to(torch.bfloat16)
+        qstart = torch.arange(batch + 1, dtype=torch.int32, device=device)
+        past = torch.full((batch,), length - 1, dtype=torch.int32, device=device)
+        slot = torch.arange(batch, dtype=torch.int32, device=device)
+        status = torch.zeros(4, dtype=torch.int32, device=device)
+        max_kv = -(-length // 64) * 64
+
+        def make(split_keys, max_splits):
+            out = torch.zeros(batch, nh * d, device=device, dtype=torch.bfloat16)
+            scratch = torch.zeros(ops.attention_generic_scratch_floats(batch, nh, d, max_splits), device=device)
+            return lambda: ops.attention_mma(True, q, out, batch, 1, nh, nkv, d, 1 / math.sqrt(d), 0, qstart, past, slot,
+                                             table, pages, kp, vp, scratch, split_keys, max_splits, status)
+
+        picked = ops.attention_mma_decode_ranges(torch.device(device), d, batch, nkv, max_kv, 512)
+        configs = [(512, -(-max_kv // 512)), picked] + [(0, n) for n in (2, 4, 8, 16) if batch * nkv * n <= 1200]
+        t = time_in_turn([make(*c) for c in configs], flush, rounds=12)
+        nbytes = 2 * batch * length * nkv * d * 2
+        cells = [f"{c}: {us:.1f} us ({nbytes / us / 1e6:.2f} TB/s)" for c, us in zip(configs, t)]
+        print(f"batch {batch} context {length} (split_keys, ranges): " + "  ".join(cells) + f"  [engine picks {picked}]",
+              flush=True)
+
+
+def sampler(cfg, device, batches: Sequence[int] = (1, 8, 64)) -> None:
+    """The sampler with and without the scratch that lets it cut rows into chunks."""
+    v = cfg.vocab_size
+    settings = [("greedy", 0.0, 0, 1.0, 0.0), ("temperature 0.7, top-k 40, top-p 0.95, min-p 0.05", 0.7, 40, 0.95, 0.05),
+                ("temperature only", 0.7, 0, 1.0, 0.0), ("top-p 0.95 only", 0.7, 0, 0.95, 0.0)]
+    for b in batches:
+        logits = torch.randn(b, v, device=device) * 3
+        req = torch.arange(b, dtype=torch.int32, device=device)
+        step = torch.zeros(b, dtype=torch.int32, device=device)
+        out = torch.empty(b, dtype=torch.int32, device=device)
+        for name, t, k, p, m in settings:
+            need = ops.sample_scratch_bytes(b, v, t, k, p, m)
+            scratch = torch.empty(need, dtype=torch.uint8, device=device) if need else None
+            one = time_in_a_row(lambda: ops.sample(logits, t, k, p, m, 1, req, step, out))
+            two = time_in_a_row(lambda: ops.sample(logits, t, k, p, m, 1, req, step, out, scratch=scratch)) if need else None
+            print(f"batch {b} vocabulary {v} {name}: one kernel {one:.1f} us" +
+                  (f", two kernels {two:.1f} us" if two is not None else ", no two-kernel path"), flush=True)
+
+
+CASES: Dict[str, Callable] = {"gemm": gemm, "decode_attention": decode_attention, "sampler": sampler}
