@@ -198,6 +198,17 @@ class PagedCache:
                 have.extend(new_pages)
                 g.page_table[slot, start:need] = torch.tensor(new_pages, dtype=torch.int32)
 
+    def release_reserved(self, slot: int) -> None:
+        """Give back the pages that ``reserve`` took beyond the sequence's committed length (a step
+        that was prepared and then not run)."""
+        keep = pages_for(self.lengths[slot])
+        for g in self.groups:
+            if g.request.kind != "kv":
+                continue
+            pages = g.pages_of_slot[slot]
+            g.pool.give_back_many(p for p in pages[keep:] if p >= 0)
+            del pages[keep:]
+
     def commit(self, slot: int, new_length: int) -> None:
         """Record the length after a step and give back pages that left every window."""
         if new_length < self.lengths[slot]:

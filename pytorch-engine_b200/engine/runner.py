@@ -64,9 +64,8 @@ class ModelRunner:
             if len(e.tokens) == 0:
                 raise ValueError(f"slot {e.slot} brings no token in this step")
             pasts.append(self.cache.length(e.slot))
-        # make room first: a failure here leaves the cache as it was
-        for e, past in zip(entries, pasts):
-            self.cache.reserve(e.slot, past + len(e.tokens))
+        # make room first: on a failure the pages taken so far go back and the cache is as it was
+        self._reserve_all([(e.slot, past + len(e.tokens)) for e, past in zip(entries, pasts)])
         ints, n_tokens, n_want = StepContext.pack_meta(entries, pasts)
         n_seqs = len(entries)
         q_lens = [len(e.tokens) for e in entries]
@@ -96,8 +95,7 @@ class ModelRunner:
         n = len(slots)
         g = self._graphs[n]
         pasts = [self.cache.length(s) for s in slots]
-        for s, past in zip(slots, pasts):
-            self.cache.reserve(s, past + 1)
+        self._reserve_all([(s, past + 1) for s, past in zip(slots, pasts)])
         g.ctx.tokens.copy_(device_tokens[:n], non_blocking=True)
         self.stager.send(list(slots) + pasts + list(range(n + 1)) + list(range(n)), g.ctx.meta[n:])
         g.graph.replay()
@@ -106,6 +104,18 @@ class ModelRunner:
             self.cache.commit(s, past + 1)
         self.steps_run += 1
         return g.logits
+
+    def _reserve_all(self, wanted) -> None:
+        """Reserve pages for every (slot, new length); all or nothing."""
+        done = []
+        try:
+            for slot, length in wanted:
+                self.cache.reserve(slot, length)
+                done.append(slot)
+        except Exception:
+            for slot in done:
+                self.cache.release_reserved(slot)
+            raise
 
     def _step_graph(self, meta_ints, n_seqs: int) -> torch.Tensor:
         g = self._graphs.get(n_seqs)

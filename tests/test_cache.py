@@ -149,3 +149,25 @@ def test_random_traffic_keeps_the_books(pe):
         c.free_slot(s)
     c.check()
     assert all(g.pool.held_count == 0 for g in c.groups if g.pool)
+
+
+def test_a_step_that_cannot_get_all_its_pages_takes_none(pe):
+    """The runner reserves for every sequence of a step or for none (no device needed: only the books)."""
+    runner_mod = __import__("importlib").import_module("pytorch-engine_b200.engine.runner")
+    c = _cache(pe, max_tokens=64 * 6, window=100)
+    a, b = c.alloc_slot(), c.alloc_slot()
+    c.reserve(a, 64); c.commit(a, 64)
+    c.reserve(b, 64); c.commit(b, 64)
+    free = c.free_pages()
+
+    class Books:
+        cache = c
+    with pytest.raises(pe.cache.CacheFull):
+        runner_mod.ModelRunner._reserve_all(Books, [(a, 64 * 3), (b, 64 * 5)])   # the second cannot be met
+    assert c.free_pages() == free and c.length(a) == 64
+    c.check()
+    runner_mod.ModelRunner._reserve_all(Books, [(a, 64 * 3), (b, 64 * 3)])
+    assert c.free_pages() == free - 4
+    c.release_reserved(a)
+    assert c.free_pages() == free - 2
+    c.check()
