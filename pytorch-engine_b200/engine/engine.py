@@ -107,7 +107,8 @@ class Engine:
                              f"{config.max_positions}")
         self.max_batch = int(max_batch)
         if max_cache_tokens is None:
-            max_cache_tokens = self.max_batch * pages_for(self.max_context_len) * PAGE_TOKENS
+            max_cache_tokens = self.default_cache_tokens(self.max_batch, self.max_context_len,
+                                                         self.model.cache_requests(), self.dtype, self.device)
         self.max_cache_tokens = int(max_cache_tokens)
         if max_slots is None:
             max_slots = max(self.max_batch, min(pages_for(self.max_cache_tokens), 4096))
@@ -127,6 +128,20 @@ class Engine:
     @classmethod
     def from_pretrained(cls, model_path: str, **kw) -> "Engine":
         return cls(model_path, **kw)
+
+    @staticmethod
+    def default_cache_tokens(max_batch: int, max_context_len: int, requests, dtype, device, free_bytes=None) -> int:
+        """``max_batch`` sequences of full length, but no more tokens than fit in four fifths of the
+        device memory that is free now (whole pages; at least one page)."""
+        want = max_batch * pages_for(max_context_len) * PAGE_TOKENS
+        per_token = sum(2 * r.kv_heads * r.head_dim for r in requests.values() if r is not None and r.kind == "kv")
+        per_token *= torch.empty((), dtype=dtype).element_size()
+        if per_token == 0:
+            return want
+        if free_bytes is None:
+            free_bytes = torch.cuda.mem_get_info(device)[0] if torch.device(device).type == "cuda" else 1 << 62
+        fit = int(free_bytes * 0.8) // per_token // PAGE_TOKENS * PAGE_TOKENS
+        return max(PAGE_TOKENS, min(want, fit))
 
     @classmethod
     def from_random(cls, config: ModelConfig, seed: int = 0, **kw) -> "Engine":

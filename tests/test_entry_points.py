@@ -91,3 +91,19 @@ def test_replayer_bookkeeping_with_a_scripted_engine(pe, tmp_path):
     assert os.path.getsize(tmp_path / "0.f32") == 12
     with pytest.raises(pe.engine.replay.TraceError):
         rp.run_step({"step": 6, "entries": [], "end": ["zz"]})
+
+
+def test_default_cache_size_is_capped_by_free_memory(pe):
+    import torch
+    CR = pe.parts.CacheRequest
+    reqs = {i: CR("kv", kv_heads=8, head_dim=128) for i in range(28)}
+    per_token = 28 * 2 * 8 * 128 * 2
+    f = pe.Engine.default_cache_tokens
+    # plenty of memory: max_batch sequences of full length, in whole pages
+    assert f(4, 100, reqs, torch.bfloat16, "cpu", free_bytes=1 << 50) == 4 * 128
+    # 64 sequences of 40,960 tokens would take 300 GB: four fifths of what is free instead, in whole pages
+    got = f(64, 40960, reqs, torch.bfloat16, "cpu", free_bytes=100 << 30)
+    assert got % 64 == 0 and got * per_token <= 0.8 * (100 << 30) < (got + 64) * per_token
+    # nothing paged: no limit from memory
+    assert f(2, 64, {0: CR("state", state_shapes=(("s", (4,), "float32"),))}, torch.float32, "cpu", free_bytes=1) == 128
+    assert f(2, 64, reqs, torch.float32, "cpu", free_bytes=10) == 64
