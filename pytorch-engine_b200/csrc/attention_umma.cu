@@ -11,8 +11,10 @@
 //             tensor memory, and O += P.V (128 x 128, four k-steps of 16 keys) with V as an MN-major
 //             operand, so the page that TMA wrote as [keys][features] needs no transpose;
 //   warps 0-3 softmax: thread r owns row r.  It reads its S row from TMEM (tcgen05.ld), scales and
-//             masks, keeps the running maximum and sum in registers, writes P as bfloat16 into shared
-//             memory in the swizzled K-major layout the MMA reads, and rescales its O row in TMEM
+//             masks, keeps the running maximum and sum in registers, writes P as bfloat16 in the
+//             swizzled K-major layout the MMA reads, into the shared memory of the page's K tile (which
+//             is spent once S is there, so P is double-buffered for free and the exponentials of one
+//             page overlap the P.V products of the page before), and rescales its O row in TMEM
 //             (tcgen05.ld / tcgen05.st) only when the maximum has grown by more than 2^8 since the last
 //             rescale (the reference of the exponentials is then moved; until then P simply carries
 //             the larger factor, which float32 sums and bfloat16 products hold without loss).
@@ -28,7 +30,6 @@ constexpr int BM = 128;        // rows per block
 constexpr int BN = 64;         // keys per page
 constexpr int kQBytes = BM * HD * 2;          // 32 KB: two 64-feature halves of [128 rows][128 B]
 constexpr int kKVBytes = 2 * BN * HD * 2;     // 32 KB: K page then V page, each two halves of [64][128 B]
-constexpr int kPBytes = BM * BN * 2;          // 16 KB
 constexpr int kTmemCols = 256;                // S0 [0,64) S1 [64,128) O [128,256)
 constexpr float kRescaleThreshold = 8.0f;     // in log2 units
 
@@ -127,17 +128,16 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
   pdl_wait();
   pdl_launch_dependents();
   char* q_s = smem;                       // [2 halves][128 rows][128 B]
-  char* kv_s = q_s + kQBytes;             // 2 stages of (K page, V page)
-  char* p_s = kv_s + 2 * kKVBytes;        // [128 rows][128 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + kPBytes);
+  char* kv_s = q_s + kQBytes;             // 2 stages of (K page, V page); P takes the K page's place once S is done
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + 2 * kKVBytes);
   uint64_t& q_full = bars[0];
   uint64_t* kv_full = bars + 1;
   uint64_t* kv_empty = bars + 3;
   uint64_t* s_full = bars + 5;
-  uint64_t& p_ready = bars[7];
-  uint64_t& pv_done = bars[8];
-  uint32_t& tmem_holder = *reinterpret_cast<uint32_t*>(bars + 9);
-  volatile int& failed = *reinterpret_cast<volatile int*>(bars + 10);
+  uint64_t* p_ready = bars + 7;   // one per stage: the softmax may be a page ahead of the P.V products
+  uint64_t& pv_done = bars[9];
+  uint32_t& tmem_holder = *reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int& failed = *reinterpret_cast<volatile int*>(bars + 11);
   if ((tma::smem_addr(smem) & 1023u) != 0) {   // the swizzled tiles need this alignment
     if (threadIdx.x == 0) report(a.status, kStatusWaitTimedOut, 29, (int)(tma::smem_addr(smem) & 1023u), 0);
     return;
@@ -165,7 +165,8 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       tma::mbar_init(&kv_empty[s], 1);
       tma::mbar_init(&s_full[s], 1);
     }
-    tma::mbar_init(&p_ready, 128);
+    tma::mbar_init(&p_ready[0], 128);
+    tma::mbar_init(&p_ready[1], 128);
     tma::mbar_init(&pv_done, 1);
     failed = 0;
     tma::fence_barrier_init();
@@ -213,7 +214,7 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
     if (lane == 0) {
       const uint32_t idesc_qk = instr_desc(BM, BN, false);
       const uint32_t idesc_pv = instr_desc(BM, HD, true);
-      const uint32_t q_addr = tma::smem_addr(q_s), p_addr = tma::smem_addr(p_s);
+      const uint32_t q_addr = tma::smem_addr(q_s);
       auto issue_qk = [&](int j) -> bool {
         const int st = j & 1;
         if (!tma::mbar_wait(&kv_full[st], (j >> 1) & 1)) return false;
@@ -233,10 +234,11 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       for (int j = 0; ok && j < n_tiles; ++j) {
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);        // S of the next page while this one's softmax runs
         if (!ok) break;
-        if (!tma::mbar_wait(&p_ready, j & 1)) { ok = false; break; }
-        fence_after_sync();
         const int st = j & 1;
-        const uint32_t v_addr = tma::smem_addr(kv_s + st * kKVBytes + kKVBytes / 2);
+        if (!tma::mbar_wait(&p_ready[st], (j >> 1) & 1)) { ok = false; break; }
+        fence_after_sync();
+        const uint32_t p_addr = tma::smem_addr(kv_s + st * kKVBytes);   // where K of this page was
+        const uint32_t v_addr = p_addr + kKVBytes / 2;
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k)
           umma_bf16(tmem_o, desc_k_major(p_addr + k * 32), desc_mn_major(v_addr + k * 16 * 128, BN * 128), idesc_pv,
@@ -267,24 +269,36 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       tmem_ld32(tmem_base + st * BN + lane_off, sv[0]);
       tmem_ld32(tmem_base + st * BN + 32 + lane_off, sv[1]);
       tmem_ld_wait();
+      // A page that every row of this block sees whole (below the diagonal, inside the window) needs
+      // no mask: the scores stay raw and the scale is folded into the exponent's multiply-add.
+      const bool whole = a.scale_log2 > 0.f && (row0 + BM <= n_rows) && (k0 + BN - 1 <= past + row0 / group) &&
+                         (a.window <= 0 || k0 > past + (row0 + BM - 1) / group - a.window);
       float mx = -INFINITY;
+      if (whole) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int kpos = k0 + h * 32 + c;
-          bool vis = live && kpos <= qpos;
-          if (a.window > 0) vis = vis && (kpos > qpos - a.window);
-          const float v = vis ? __uint_as_float(sv[h][c]) * a.scale_log2 : -INFINITY;
-          sv[h][c] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
-      // the previous P.V must be done before P is overwritten or O is touched
-      if (j > 0 && !tma::mbar_wait(&pv_done, (j - 1) & 1)) { ok = false; break; }
-      fence_after_sync();
+          for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sv[h][c]));
+        mx *= a.scale_log2;   // the scale is positive
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int kpos = k0 + h * 32 + c;
+            bool vis = live && kpos <= qpos;
+            if (a.window > 0) vis = vis && (kpos > qpos - a.window);
+            const float v = vis ? __uint_as_float(sv[h][c]) * a.scale_log2 : -INFINITY;
+            sv[h][c] = __float_as_uint(v);
+            mx = fmaxf(mx, v);
+          }
+      }
       // move the reference of the exponentials only when the maximum has grown a lot
       const bool grow = mx > m_ref + kRescaleThreshold;
       if (__any_sync(0xffffffffu, grow && j > 0 && m_ref != -INFINITY)) {
+        // O is rescaled in place: the previous P.V must be done with it first
+        if (!tma::mbar_wait(&pv_done, (j - 1) & 1)) { ok = false; break; }
+        fence_after_sync();
         const float f = (grow && m_ref != -INFINITY) ? fast_exp2(m_ref - mx) : 1.0f;
 #pragma unroll 1
         for (int c = 0; c < HD; c += 32) {
@@ -301,26 +315,35 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       if (grow) m_ref = mx;
       const float base = (m_ref == -INFINITY) ? 0.f : m_ref;
       float sum = 0.f;
-      char* prow = p_s + r * 128;
+      char* prow = kv_s + st * kKVBytes + r * 128;   // K of this page is spent (S is done): P takes its place
+      // P = exp2(score - reference), as bfloat16 into the swizzled operand tile, 8 keys per 16-byte store
+      auto exps = [&](auto exponent) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {   // 16-byte chunks of 8 keys
-          uint32_t w[4];
+          for (int c8 = 0; c8 < 4; ++c8) {
+            uint32_t w[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float p0 = fast_exp2(__uint_as_float(sv[h][c8 * 8 + 2 * i]) - base);
-            const float p1 = fast_exp2(__uint_as_float(sv[h][c8 * 8 + 2 * i + 1]) - base);
-            sum += p0 + p1;
-            w[i] = pack2(p0, p1);
+            for (int i = 0; i < 4; ++i) {
+              const float p0 = fast_exp2(exponent(__uint_as_float(sv[h][c8 * 8 + 2 * i])));
+              const float p1 = fast_exp2(exponent(__uint_as_float(sv[h][c8 * 8 + 2 * i + 1])));
+              sum += p0 + p1;
+              w[i] = pack2(p0, p1);
+            }
+            const int chunk = h * 4 + c8;
+            *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          const int chunk = h * 4 + c8;
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
+      };
+      if (whole) {
+        const float sc = a.scale_log2, nb = -base;
+        exps([sc, nb](float s) { return fmaf(s, sc, nb); });
+      } else {
+        exps([base](float s) { return s - base; });
+      }
       l += sum;
       tma::fence_proxy_async();           // P must be visible to the tensor core's reads
       fence_before_sync();
-      tma::mbar_arrive(&p_ready);
+      tma::mbar_arrive(&p_ready[st]);
     }
     if (ok && tma::mbar_wait(&pv_done, (n_tiles - 1) & 1)) {
       fence_after_sync();
@@ -398,7 +421,7 @@ extern "C" int pe_attention_umma_prefill(const void* q, long long q_ld, long lon
   int me = pe::tma::make_map_2d_bf16(&kmap, k_pages, HD, rows, HD, 64, BN);
   if (me == 0) me = pe::tma::make_map_2d_bf16(&vmap, v_pages, HD, rows, HD, 64, BN);
   if (me != 0) return me < 0 ? me : PE_ERR_BAD_ARGUMENT;
-  const size_t smem = kQBytes + 2 * kKVBytes + kPBytes + 128;
+  const size_t smem = kQBytes + 2 * kKVBytes + 128;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t ce = cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -78,6 +78,36 @@ def gemm(cfg, device, rows: Sequence[int] = (2048, 4096, 1024)) -> None:
     print("status word", status.tolist(), flush=True)
 
 
+def prefill_attention(cfg, device, lengths: Sequence[int] = (2048, 4096, 8192, 512)) -> None:
+    """One prompt through the tcgen05 prefill attention and through the mma.sync one."""
+    nh, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    for t in lengths:
+        pages = (t + 63) // 64 + 2
+        kp = (torch.randn(pages, nkv, 64, d, device=device) * 0.5).to(torch.bfloat16)
+        vp = (torch.randn(pages, nkv, 64, d, device=device) * 0.5).to(torch.bfloat16)
+        table = torch.arange(pages, dtype=torch.int32, device=device).view(1, -1)
+        q = torch.randn(t, (nh + 2 * nkv) * d, device=device).to(torch.bfloat16)
+        out1 = torch.zeros(t, nh * d, device=device, dtype=torch.bfloat16)
+        out2 = torch.zeros_like(out1)
+        qstart = torch.tensor([0, t], dtype=torch.int32, device=device)
+        past = torch.zeros(1, dtype=torch.int32, device=device)
+        slot = torch.zeros(1, dtype=torch.int32, device=device)
+        status = torch.zeros(4, dtype=torch.int32, device=device)
+        sc = 1 / math.sqrt(d)
+        flops = 2.0 * nh * d * t * t     # causal: half of 4 * heads * d * t^2
+        line = f"{t} tokens, {nh} x {nkv} heads, d={d}:"
+        if ops.attention_umma_supported(torch.bfloat16, d, nh, nkv):
+            us = time_in_a_row(lambda: ops.attention_umma_prefill(q, out1, 1, t, nh, nkv, d, sc, 0, qstart, past, slot, table,
+                                                                  pages, kp, vp, status), calls=10)
+            line += f"  tcgen05 {us:.1f} us ({flops / us / 1e6:.0f} TFLOP/s)"
+        if ops.attention_mma_supported(torch.bfloat16, d, nh, nkv):
+            us = time_in_a_row(lambda: ops.attention_mma(False, q, out2, 1, t, nh, nkv, d, sc, 0, qstart, past, slot, table,
+                                                         pages, kp, vp, None, 0, 0, status), calls=10)
+            line += f"  mma.sync {us:.1f} us ({flops / us / 1e6:.0f} TFLOP/s)"
+            line += f"  max difference {float((out1.float() - out2.float()).abs().max()):.2e}"
+        print(line + f"  status {status.tolist()[0]}", flush=True)
+
+
 def decode_attention(cfg, device, cases: Sequence[Sequence[int]] = ((8, 4090), (1, 4090), (16, 4090), (64, 4090))) -> None:
     """Split + merge decode attention with ranges of 512 keys, the ranges the engine picks, and other even splits."""
     nh, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
@@ -129,4 +159,4 @@ def sampler(cfg, device, batches: Sequence[int] = (1, 8, 64)) -> None:
                   (f", two kernels {two:.1f} us" if two is not None else ", no two-kernel path"), flush=True)
 
 
-CASES: Dict[str, Callable] = {"gemm": gemm, "decode_attention": decode_attention, "sampler": sampler}
+CASES: Dict[str, Callable] = {"gemm": gemm, "prefill_attention": prefill_attention, "decode_attention": decode_attention, "sampler": sampler}
