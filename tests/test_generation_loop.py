@@ -74,7 +74,7 @@ def test_batches_follow_one_another_and_reuse_slots(pe):
     assert {s for st in be.steps for s, _, _ in st} == {0, 1, 2}   # the same slots again
 
 
-def test_page_budget_splits_batches(pe):
+def test_page_limit_splits_batches(pe):
     be = FakeBackend({i: [1] * 40 for i in range(4)}, pages=3)
     lp = _loop(pe, be, max_batch=8, max_context=200)
     params = pe.SamplingParams(max_tokens=30, temperature=0.0)
