@@ -290,6 +290,57 @@ def test_attention_finds_a_far_key(ops, decode, dtype):
         assert torch.allclose(got[h], v_far[h // 2], atol=1e-4 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize("kernel,decode", [("generic_f32", False), ("generic_f32", True), ("generic_bf16", False),
+                                           ("generic_bf16", True), ("mma", False), ("mma", True), ("umma", False)])
+def test_attention_at_the_windows_edge(ops, kernel, decode):
+    """Two keys match the query strongly: the last one outside the window of the last query and the
+    first one inside it.  With an edge off by one either way the output changes by tens."""
+    dtype = torch.float32 if kernel == "generic_f32" else torch.bfloat16
+    nh, nkv, d = (8, 2, 128) if kernel in ("mma", "umma") else (4, 2, 32)
+    L, W = 200, 50
+    outside, inside = L - 1 - W, L - W            # positions 149 and 150 for the query at 199
+    ps = PagedSetup([L], nkv, d, dtype, seed=21, key_scale=0.05)
+    probe = torch.randn(d)
+    probe = probe / probe.norm() * 12.0
+    for pos, value in ((outside, 50.0), (inside, -30.0)):
+        page = int(ps.table[ps.slots[0], pos // 64])
+        ps.k_pages[page, :, pos % 64] = (probe * 2.0).to(DEV, dtype)
+        ps.v_pages[page, :, pos % 64] = value
+        ps.k[0][pos] = (probe * 2.0).to(dtype)
+        ps.v[0][pos] = value
+    n_q = 1 if decode else L
+    past = L - n_q
+    q = probe.repeat(n_q, nh).contiguous()          # every query matches the two keys
+    ld = nh * d + 2 * nkv * d
+    q_all = torch.zeros(n_q, ld)
+    q_all[:, : nh * d] = q
+    q_all = q_all.to(DEV, dtype)
+    out = torch.zeros(n_q, nh * d, device=DEV, dtype=dtype)
+    qstart = torch.tensor([0, n_q], dtype=torch.int32, device=DEV)
+    past_t = torch.tensor([past], dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    scratch = torch.zeros(ops.attention_generic_scratch_floats(1, nh, d, 4), device=DEV) if decode else None
+    split = (64, 4) if decode else (0, 0)
+    st = _status()
+    if kernel == "umma":
+        ops.attention_umma_prefill(q_all, out, 1, n_q, nh, nkv, d, scale, W, qstart, past_t, ps.seq_slot, ps.table,
+                                   ps.num_pages, ps.k_pages, ps.v_pages, st)
+    else:
+        fn = ops.attention_mma if kernel == "mma" else ops.attention_generic
+        fn(decode, q_all, out, 1, n_q, nh, nkv, d, scale, W, qstart, past_t, ps.seq_slot, ps.table, ps.num_pages,
+           ps.k_pages, ps.v_pages, scratch, split[0], split[1], st)
+    assert st.tolist()[0] == 0
+    got = out.float().cpu().view(n_q, nh, d)
+    want = plain.causal_gqa_attention(q.view(n_q, nh, d).float(), ps.k[0].float(), ps.v[0].float(), scale, window=W,
+                                      q_start=past)
+    tol = 1e-3 if dtype == torch.float32 else 0.3
+    assert float((got - want).abs().max()) < tol
+    # the last query sees the inside key only, the one before it both
+    assert abs(float(got[-1].mean()) + 30.0) < 0.5
+    if not decode:
+        assert abs(float(got[-2].mean()) - 10.0) < 0.5
+
+
 MMA_SHAPES = [(8, 2, 64), (32, 8, 128), (16, 1, 128), (3, 3, 64), (6, 2, 128), (10, 2, 64)]
 
 
