@@ -30,8 +30,11 @@ namespace umma2 {
 constexpr int BM = 128;        // rows of x per block (the pair: 256)
 constexpr int BN = 256;        // accumulator columns
 constexpr int BNH = 128;       // rows of W per block
-constexpr int BK = 64, STAGES = 6;
-constexpr int kBytesA = BM * BK * 2, kBytesB = BNH * BK * 2, kStage = kBytesA + kBytesB;
+constexpr int BK = 64;
+constexpr int KBS = 2;         // k blocks per stage: one 3-D TMA copy per operand brings both
+constexpr int STAGES = 3;
+constexpr int kTileA = BM * BK * 2, kTileB = BNH * BK * 2;   // one k block of each operand
+constexpr int kBytesA = KBS * kTileA, kBytesB = KBS * kTileB, kStage = kBytesA + kBytesB;
 constexpr int kTmemCols = 512;
 constexpr int kThreads = 192;
 
@@ -72,10 +75,27 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
 }
 // a box into this block's shared memory, its bytes counted on a barrier that may be the peer's
-__device__ __forceinline__ void load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster_addr) {
+// The operands are seen as [k block][row][64] (K is a multiple of 64), so that one copy brings KBS k
+// blocks of a slice of rows as KBS consecutive K-major swizzled tiles: a thread can issue a copy only
+// every ~150 ns, which two copies per k block of 0.3 us would leave no room for.
+__device__ __forceinline__ void load_3d_pair(void* dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar_cluster_addr) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-      ::"r"(tma::smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr) : "memory");
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+      ::"r"(tma::smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar_cluster_addr) : "memory");
+}
+static int make_map_kblocks(CUtensorMap* map, const void* base, uint64_t K, uint64_t rows, uint64_t row_stride_elems,
+                            uint32_t box_rows, uint32_t kbs) {
+  tma::EncodeTiledFn fn = tma::encode_fn();
+  if (fn == nullptr) return -5;
+  if (((uintptr_t)base % 16) || ((row_stride_elems * 2) % 16) || box_rows > 256 || (K % BK)) return -2;
+  cuuint64_t dims[3] = {BK, rows, K / BK};
+  cuuint64_t strides[2] = {row_stride_elems * 2, BK * 2};
+  cuuint32_t box[3] = {BK, box_rows, kbs};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* holder_smem, uint32_t cols) {
@@ -143,7 +163,8 @@ gemm_umma2_kernel(Params p, const __grid_constant__ CUtensorMap amap, const __gr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
   const bool leader = rank == 0;
-  const int k_blocks = (p.K + BK - 1) / BK;
+  const int k_blocks = p.K / BK;
+  const int k_steps = (k_blocks + KBS - 1) / KBS;
   const int n_tiles_total = p.m_tiles * p.n_tiles;
   const int first_tile = (int)cluster_id_x(), tile_step = (int)n_clusters_x();
 
@@ -177,9 +198,9 @@ gemm_umma2_kernel(Params p, const __grid_constant__ CUtensorMap amap, const __gr
         const int m0 = (tile % p.m_tiles) * (2 * BM) + (int)rank * BM;
         const int nt = tile / p.m_tiles;
         const int b_row = p.mode == 2 ? nt * BNH + (leader ? 0 : p.pair_offset) : nt * BN + (int)rank * BNH;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int ks = 0; ks < k_steps; ++ks) {
           if (!tma::mbar_wait(&empty_bar[stage], phase ^ 1)) {
-            report(p.status, kStatusWaitTimedOut, 20, tile, kb);
+            report(p.status, kStatusWaitTimedOut, 20, tile, ks);
             failed = 1;
             break;
           }
@@ -187,8 +208,8 @@ gemm_umma2_kernel(Params p, const __grid_constant__ CUtensorMap amap, const __gr
           char* sb = sa + kBytesA;
           if (leader) tma::mbar_expect_tx(&full_bar[stage], 2 * kStage);
           const uint32_t bar = map_to_rank(tma::smem_addr(&full_bar[stage]), 0);
-          load_2d_pair(sa, &amap, kb * BK, m0, bar);
-          load_2d_pair(sb, &bmap, kb * BK, b_row, bar);
+          load_3d_pair(sa, &amap, 0, m0, ks * KBS, bar);      // k blocks beyond K arrive as zeros and still count
+          load_3d_pair(sb, &bmap, 0, b_row, ks * KBS, bar);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -209,18 +230,21 @@ gemm_umma2_kernel(Params p, const __grid_constant__ CUtensorMap amap, const __gr
         }
         fence_after_sync();
         const uint32_t d_tmem = tmem_base + ab * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int ks = 0; ks < k_steps; ++ks) {
           if (!tma::mbar_wait(&full_bar[stage], phase)) {
-            report(p.status, kStatusWaitTimedOut, 22, tile, kb);
+            report(p.status, kStatusWaitTimedOut, 22, tile, ks);
             failed = 1;
             break;
           }
           fence_after_sync();
           const uint32_t sa = tma::smem_addr(smem + stage * kStage);
           const uint32_t sb = sa + kBytesA;
+          const int n_kb = min(KBS, k_blocks - ks * KBS);
+          for (int j = 0; j < n_kb; ++j)
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_bf16_pair(d_tmem, smem_desc(sa + k * 32), smem_desc(sb + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < BK / 16; ++k)
+              umma_bf16_pair(d_tmem, smem_desc(sa + j * kTileA + k * 32), smem_desc(sb + j * kTileB + k * 32), idesc,
+                             (ks > 0 || j > 0 || k > 0) ? 1u : 0u);
           umma_commit_both(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -326,12 +350,12 @@ gemm_umma2_kernel(Params p, const __grid_constant__ CUtensorMap amap, const __gr
 }  // namespace pe
 
 extern "C" int pe_gemm_umma2_supported(int M, int N, int K, int pair_offset) {
-  if (M < 1 || N < 1 || K < 8 || (K % 8)) return 0;
+  if (M < 1 || N < 1 || K < 64 || (K % 64)) return 0;   // whole k blocks (the copies' 3-D view needs it)
   if (pair_offset > 0 && (N % 128 || pair_offset != N)) return 0;
   return 1;
 }
 
-// The arguments of pe_gemm_umma (gemm_umma.cu); n_sms is rounded down to pairs.
+// The arguments of pe_gemm_umma (gemm_umma.cu); n_sms is rounded down to pairs; K a multiple of 64.
 extern "C" int pe_gemm_umma2(const void* x, long long ldx, const void* w, void* y, long long ldy, int M, int N, int K,
                              int out_f32, int pair_offset, int n_sms, int* status, cudaStream_t stream) {
   using namespace pe::umma2;
@@ -347,8 +371,8 @@ extern "C" int pe_gemm_umma2(const void* x, long long ldx, const void* w, void* 
   p.n_tiles = (N + p.n_per_tile - 1) / p.n_per_tile;
   CUtensorMap amap, bmap;
   const uint64_t w_rows = pair_offset > 0 ? 2ull * N : (uint64_t)N;
-  int e = pe::tma::make_map_2d_bf16(&amap, x, K, M, ldx, BK, BM);
-  if (e == 0) e = pe::tma::make_map_2d_bf16(&bmap, w, K, w_rows, K, BK, BNH);
+  int e = make_map_kblocks(&amap, x, K, M, ldx, BM, KBS);
+  if (e == 0) e = make_map_kblocks(&bmap, w, K, w_rows, K, BNH, KBS);
   if (e != 0) return e < 0 ? e : PE_ERR_BAD_ARGUMENT;
   const size_t smem = 1024 + (size_t)STAGES * kStage;
   static bool attr_set = false;

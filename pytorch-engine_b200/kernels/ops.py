@@ -222,9 +222,17 @@ def gemm_umma(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, status: 
     _count(1)
 
 
+def gemm_umma2_supported(x: torch.Tensor, weight: torch.Tensor, pair_offset: int = 0) -> bool:
+    """Whether csrc/gemm_umma2.cu takes the product: as ``gemm_umma_supported``, and K % 64 == 0."""
+    if not gemm_umma_supported(x, weight, pair_offset):
+        return False
+    n = weight.shape[0] // 2 if pair_offset else weight.shape[0]
+    return bool(library().pe_gemm_umma2_supported(x.shape[0], n, x.shape[1], pair_offset))
+
+
 def gemm_umma2(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, status: torch.Tensor, pair_offset: int = 0) -> None:
     """``gemm_umma`` with two SMs per 256 x 256 output tile (csrc/gemm_umma2.cu, tcgen05 cta_group::2)."""
-    _need(gemm_umma_supported(x, weight, pair_offset), "gemm_umma2: needs bfloat16, K % 8 == 0, dense weight rows")
+    _need(gemm_umma2_supported(x, weight, pair_offset), "gemm_umma2: needs bfloat16, K % 64 == 0, dense weight rows")
     _need(out.stride(-1) == 1 and out.dtype in (torch.bfloat16, torch.float32), "gemm_umma2: out bfloat16 or float32")
     m, k = x.shape
     n = out.shape[1]

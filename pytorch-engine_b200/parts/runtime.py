@@ -160,7 +160,8 @@ class Runtime:
                 out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
             # two SMs per 256 x 256 tile (csrc/gemm_umma2.cu): measured 3-6 % faster than one SM per
             # 128 x 256 tile on the plain products; the fused gate|up product stays on gemm_umma.cu
-            (ops.gemm_umma2 if self.pair_gemm else ops.gemm_umma)(x, weight, out, self.status)
+            pair = self.pair_gemm and ops.gemm_umma2_supported(x, weight)
+            (ops.gemm_umma2 if pair else ops.gemm_umma)(x, weight, out, self.status)
             return out
         if self.takes_small_gemm(x, weight):
             # a handful of rows: the package's weight-streaming kernel (csrc/gemm_smallm.cu)

