@@ -82,6 +82,14 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// silu(g) * u for an epilogue that rounds its result to bfloat16: the exponential and the reciprocal are
+// the hardware approximations (about 2 ulp each, far inside bfloat16's 8 bits).  With expf and an IEEE
+// division the epilogue of the fused gate|up product took longer than the tile's matrix products
+// (358 us against 260 us for 2,048 rows of the 8B shape).  Large |g|: exp(-g) = inf gives -0, = 0 gives g.
+__device__ __forceinline__ float silu_mul_fast(float g, float u) {
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
 // ---- reductions --------------------------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -251,7 +251,7 @@ gemm_skinny_kernel(Params p, const __grid_constant__ CUtensorMap xmap, const __g
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float g = __uint_as_float(v[j]);
-          o[j] = p.mode == 2 ? g / (1.0f + expf(-g)) * __uint_as_float(u[j]) : g;
+          o[j] = p.mode == 2 ? silu_mul_fast(g, __uint_as_float(u[j])) : g;
         }
         const bool whole = n0 + c + 8 <= p.N;
         if (p.mode == 1) {

@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(WARPS * 32, NT == 1 ? 16 / WARPS : 1) gemm_sma
       float v = c[n][e];
       if (PAIR) {
         const float up = c[NT + n][e];
-        v = v / (1.0f + expf(-v)) * up;
+        v = sizeof(OutT) == 2 ? silu_mul_fast(v, up) : v / (1.0f + expf(-v)) * up;   // exact for a float32 result
       }
       store_out<OutT>(y + (size_t)m * a.ldy + col, v);
     }

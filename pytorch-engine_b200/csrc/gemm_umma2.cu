@@ -281,8 +281,8 @@ gemm_umma2_kernel(Params p, const __grid_constant__ CUtensorMap amap, const __gr
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
-              const float v0 = g0 / (1.0f + expf(-g0)) * __uint_as_float(u[2 * j]);
-              const float v1 = g1 / (1.0f + expf(-g1)) * __uint_as_float(u[2 * j + 1]);
+              const float v0 = silu_mul_fast(g0, __uint_as_float(u[2 * j]));
+              const float v1 = silu_mul_fast(g1, __uint_as_float(u[2 * j + 1]));
               o[j] = pack2(v0, v1);
             }
             if (n0 + c + 32 <= p.N && (p.ldy % 8) == 0) {

@@ -42,7 +42,9 @@ class SwiGLU:
             ops.gemm_skinny(x, self.gate_up, act, rt.status, pair_offset=self.intermediate)
         elif rt.takes_large_gemm(x, self.gate_up, self.intermediate):
             # tcgen05 product over [gate rows | matching up rows] tiles, gate applied on the way out of TMEM
-            ops.gemm_umma(x, self.gate_up, act, rt.status, pair_offset=self.intermediate)
+            # many rows: a pair of SMs per tile where the kernel takes the shape (K a multiple of 64)
+            pair = rt.pair_gemm and x.shape[0] >= rt.large_gemm_rows and ops.gemm_umma2_supported(x, self.gate_up, self.intermediate)
+            (ops.gemm_umma2 if pair else ops.gemm_umma)(x, self.gate_up, act, rt.status, pair_offset=self.intermediate)
         else:
             gu = ctx.buffer("ffn.gate_up", (n, 2 * self.intermediate), rt.dtype)
             rt.linear(x, self.gate_up, out=gu)
