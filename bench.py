@@ -2,7 +2,7 @@
 """Benchmark: decode tokens/s of a Qwen3-8B-shaped model (random weights, bfloat16) on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --micro gemm|gemm_skinny|prefill_attention|decode_attention|sampler     (single kernels, text output)
+    python bench.py --micro gemm|prefill_attention|decode_attention|sampler     (single kernels, text output)
 
 A step is one decode step: every live sequence gets one token (model step + sampler).  The default
 run has the layer sizes of the Qwen3-8B shape, a batch of 8 and a context of 4,096.  One JSON line
@@ -138,7 +138,7 @@ def main():
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--micro", type=str, default=None,
-                    help="time single kernels at the preset's sizes instead (gemm, gemm_skinny, prefill_attention, decode_attention, sampler) and print text")
+                    help="time single kernels at the preset's sizes instead (gemm, prefill_attention, decode_attention, sampler) and print text")
     args = ap.parse_args()
 
     if args.impl == "reference":

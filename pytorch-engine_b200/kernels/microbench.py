@@ -78,33 +78,6 @@ def gemm(cfg, device, rows: Sequence[int] = (2048, 4096, 1024)) -> None:
     print("status word", status.tolist(), flush=True)
 
 
-def gemm_skinny(cfg, device, rows: Sequence[int] = (16, 32, 64, 128)) -> None:
-    """The product for 9..128 rows (narrow weight slices, every SM streams its share) against the library
-    product and, for the fused gate|up product, the many-row tcgen05 kernel."""
-    status = torch.zeros(4, dtype=torch.int32, device=device)
-    flush = _flush_buffer(device)
-    h, i = cfg.hidden_size, cfg.intermediate_size
-    qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
-    shapes = [("q|k|v", qkv, h, 0), ("o", h, cfg.num_attention_heads * cfg.head_dim, 0), ("gate|up fused", i, h, 1),
-              ("down", h, i, 0), ("logits", cfg.vocab_size, h, 0)]
-    for m in rows:
-        for name, n, k, pair in shapes:
-            x = torch.randn(m, k, device=device).to(torch.bfloat16)
-            w = torch.randn(2 * n if pair else n, k, device=device).to(torch.bfloat16)
-            out = torch.empty(m, n, device=device, dtype=torch.bfloat16)
-            nbytes = w.numel() * 2
-            fns = [lambda: ops.gemm_skinny(x, w, out, status, pair_offset=n if pair else 0)]
-            if pair:
-                fns.append(lambda: ops.gemm_umma(x, w, out, status, pair_offset=n))
-            else:
-                fns.append(lambda: torch.mm(x, w.T))
-            t = time_in_turn(fns, flush)
-            other = "tcgen05 many-row kernel" if pair else "library"
-            print(f"M={m} {name} N={n} K={k}: narrow slices {t[0]:.1f} us ({nbytes / t[0] / 1e6:.2f} TB/s)  "
-                  f"{other} {t[1]:.1f} us ({nbytes / t[1] / 1e6:.2f} TB/s)", flush=True)
-    print("status word", status.tolist(), flush=True)
-
-
 def prefill_attention(cfg, device, lengths: Sequence[int] = (2048, 4096, 8192, 512)) -> None:
     """One prompt through the tcgen05 prefill attention and through the mma.sync one."""
     nh, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
@@ -186,4 +159,4 @@ def sampler(cfg, device, batches: Sequence[int] = (1, 8, 64)) -> None:
                   (f", two kernels {two:.1f} us" if two is not None else ", no two-kernel path"), flush=True)
 
 
-CASES: Dict[str, Callable] = {"gemm": gemm, "gemm_skinny": gemm_skinny, "prefill_attention": prefill_attention, "decode_attention": decode_attention, "sampler": sampler}
+CASES: Dict[str, Callable] = {"gemm": gemm, "prefill_attention": prefill_attention, "decode_attention": decode_attention, "sampler": sampler}

@@ -245,32 +245,6 @@ def gemm_umma2(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, status:
     _count(1)
 
 
-def gemm_skinny_supported(x: torch.Tensor, weight: torch.Tensor, pair_offset: int = 0) -> bool:
-    """Whether csrc/gemm_skinny.cu (tcgen05, narrow weight slices so that every SM streams its share)
-    takes ``x [M, K] @ weight^T``: bfloat16, M <= 128, K % 8 == 0."""
-    if not (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
-            and x.stride(0) % 8 == 0 and weight.is_contiguous() and x.data_ptr() % 16 == 0):
-        return False
-    n = weight.shape[0] // 2 if pair_offset else weight.shape[0]
-    return bool(library().pe_gemm_skinny_supported(x.shape[0], n, x.shape[1], pair_offset))
-
-
-def gemm_skinny(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, status: torch.Tensor, pair_offset: int = 0) -> None:
-    """``out[M, N] = x @ weight^T`` for up to 128 rows (out bfloat16 or float32); with ``pair_offset`` = I:
-    ``out[M, I] = silu(x @ gate^T) * (x @ up^T)`` for weight = [gate; up]."""
-    _need(gemm_skinny_supported(x, weight, pair_offset), "gemm_skinny: needs bfloat16, M <= 128, K % 8 == 0, dense weight rows")
-    _need(out.stride(-1) == 1 and out.dtype in (torch.bfloat16, torch.float32), "gemm_skinny: out bfloat16 or float32")
-    m, k = x.shape
-    n = out.shape[1]
-    _need(weight.shape[1] == k and weight.shape[0] == (2 * n if pair_offset else n) and out.shape[0] == m,
-          "gemm_skinny: shapes do not match")
-    _need(not pair_offset or out.dtype == torch.bfloat16, "gemm_skinny: the fused gate writes bfloat16")
-    check(library().pe_gemm_skinny(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), out.stride(0), m, n, k,
-                                   1 if out.dtype == torch.float32 else 0, pair_offset, sm_count(x.device), _ptr(status),
-                                   _stream()), "gemm_skinny")
-    _count(1)
-
-
 def attention_mma_decode_ranges(device: torch.device, head_dim: int, n_seqs: int, n_kv_heads: int, max_kv_len: int,
                                 split_keys: int) -> tuple:
     """(split_keys, max_splits) for the tensor-core decode attention.  When one wave of blocks can

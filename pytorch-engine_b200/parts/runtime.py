@@ -104,13 +104,6 @@ class Runtime:
         return (self.own_small_gemm and x.dim() == 2 and x.shape[0] <= self.small_gemm_rows
                 and ops.gemm_smallm_supported(x, weight))
 
-    def takes_skinny_pair_gemm(self, x: torch.Tensor, weight: torch.Tensor, pair_offset: int) -> bool:
-        """The fused gate|up product for 9..128 rows runs on csrc/gemm_skinny.cu (measured 8-10 % faster
-        there than on the many-row kernel; for plain products of that size the library is faster, since
-        without multicast every SM has to take in all of x next to its narrow slice of weights)."""
-        return (self.own_large_gemm and pair_offset > 0 and x.dim() == 2 and self.small_gemm_rows < x.shape[0] <= 128
-                and ops.gemm_skinny_supported(x, weight, pair_offset))
-
     def takes_large_gemm(self, x: torch.Tensor, weight: torch.Tensor, pair_offset: int = 0) -> bool:
         rows = 9 if pair_offset else self.large_gemm_rows   # the fused gate wins at every size above the small kernel's
         return (self.own_large_gemm and x.dim() == 2 and x.shape[0] >= rows

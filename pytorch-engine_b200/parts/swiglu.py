@@ -37,9 +37,6 @@ class SwiGLU:
         if rt.takes_small_gemm(x, self.gate_up):
             # few rows: gate|up product with silu(gate) * up in its epilogue
             ops.gemm_smallm(x, self.gate_up, act, pair_offset=self.intermediate)
-        elif rt.takes_skinny_pair_gemm(x, self.gate_up, self.intermediate):
-            # a few dozen rows: narrow weight slices so that every SM streams its share (tcgen05, M = 64 or 128)
-            ops.gemm_skinny(x, self.gate_up, act, rt.status, pair_offset=self.intermediate)
         elif rt.takes_large_gemm(x, self.gate_up, self.intermediate):
             # tcgen05 product over [gate rows | matching up rows] tiles, gate applied on the way out of TMEM
             # many rows: a pair of SMs per tile where the kernel takes the shape (K a multiple of 64)

@@ -570,43 +570,6 @@ def test_gemm_umma_with_the_gate_fused(ops, M, I, K, kernel):
     assert rel_err(out.float().cpu(), want) < KTOL[torch.bfloat16]
 
 
-@pytest.mark.parametrize("M,N,K", [(9, 256, 64), (64, 1536, 1024), (128, 640, 2048), (17, 515, 192), (100, 1000, 4096),
-                                   (33, 4096, 320), (1, 128, 64), (48, 130, 12288), (65, 40000, 128), (64, 6144, 576)])
-def test_gemm_skinny(ops, M, N, K):
-    """The product for up to 128 rows: rows of x as the MMA's M side (64 or 128), narrow slices of W."""
-    torch.manual_seed(33)
-    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
-    w = (torch.randn(N, K, device=DEV) * 0.5).to(torch.bfloat16)
-    want = x.float().cpu() @ w.float().cpu().T
-    st = _status()
-    out32 = torch.full((M, N), float("nan"), device=DEV)
-    ops.gemm_skinny(x, w, out32, st)
-    assert st.tolist()[0] == 0
-    assert rel_err(out32.cpu(), want) < 2e-5
-    out16 = torch.zeros(M, N + 8, device=DEV, dtype=torch.bfloat16)[:, :N]
-    ops.gemm_skinny(x, w, out16, st)
-    assert rel_err(out16.float().cpu(), want) < KTOL[torch.bfloat16]
-    wide = torch.randn(M, K + 24, device=DEV).to(torch.bfloat16)
-    ops.gemm_skinny(wide[:, :K], w, out32, st)
-    assert rel_err(out32.cpu(), wide[:, :K].float().cpu() @ w.float().cpu().T) < 2e-5
-    assert st.tolist()[0] == 0
-
-
-@pytest.mark.parametrize("M,I,K", [(9, 64, 64), (64, 384, 1024), (128, 1280, 512), (20, 4096, 192), (64, 12288, 256)])
-def test_gemm_skinny_with_the_gate_fused(ops, M, I, K):
-    torch.manual_seed(34)
-    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
-    w = (torch.randn(2 * I, K, device=DEV) * (2.0 / K ** 0.5)).to(torch.bfloat16)
-    gu = x.float().cpu() @ w.float().cpu().T
-    g, u = gu[:, :I], gu[:, I:]
-    want = g / (1 + torch.exp(-g)) * u
-    out = torch.zeros(M, I, device=DEV, dtype=torch.bfloat16)
-    st = _status()
-    ops.gemm_skinny(x, w, out, st, pair_offset=I)
-    assert st.tolist()[0] == 0
-    assert rel_err(out.float().cpu(), want) < KTOL[torch.bfloat16]
-
-
 def test_sampler_greedy_and_ties(ops):
     torch.manual_seed(8)
     logits = torch.randn(6, 1000, device=DEV)
