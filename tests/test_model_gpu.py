@@ -381,3 +381,34 @@ def test_trace_run_program(pe, model_folders, oracles, tmp_path, dtype):
     assert read(0).shape == (3, V) and read(1).shape == (1, V)
     want = {k: (ra if k[0] == "a" else rb)[k[1]] for k in got}
     _check(got, want, dtype, "trace_run")
+
+
+@pytest.mark.parametrize("hidden,inter,heads,kv,d,window", [(256, 384, 4, 2, 128, None), (200, 328, 6, 2, 64, 300),
+                                                           (320, 640, 2, 1, 128, 700)])
+def test_a_prompt_of_more_than_a_thousand_tokens(pe, hidden, inter, heads, kv, d, window):
+    """Prompts this long take the many-row kernels (the tcgen05 products where K is a multiple of 64,
+    the tcgen05 attention at head size 128): a long and a short prompt in one step, then single tokens,
+    at the first, a middle and the last position of the long prompt."""
+    cfgd = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=hidden, num_attention_heads=heads,
+                num_key_value_heads=kv, head_dim=d, intermediate_size=inter, vocab_size=515, rope_theta=1e6,
+                rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=2048)
+    if window:
+        cfgd.update(use_sliding_window=True, sliding_window=window, max_window_layers=1)
+    cfg = pe.Qwen3Config.from_dict(cfgd)
+    eng = pe.Engine.from_random(cfg, seed=5, dtype="bfloat16", max_context_len=2048, max_cache_tokens=4096, max_batch=2)
+    w = {k: v.float().cpu() for k, v in pe.weights.random_weights(eng.plan, 5, device="cuda:0").items()}
+    lens = [1100, 70]
+    seqs = [_tokens(515, L + 3, 40 + i) for i, L in enumerate(lens)]
+    wants = [(0, 600, 1099), (69,)]
+    slots = [eng.alloc_slot(), eng.alloc_slot()]
+    lg = eng.step([pe.StepEntry(s, q[:L], wt) for s, q, L, wt in zip(slots, seqs, lens, wants)]).float().cpu()
+    got = [[lg[0], lg[1], lg[2]], [lg[3]]]
+    for t in range(3):
+        lg = eng.step([pe.StepEntry(s, [q[L + t]], (0,)) for s, q, L in zip(slots, seqs, lens)]).float().cpu()
+        got[0].append(lg[0]); got[1].append(lg[1])
+    for s in slots:
+        eng.free_slot(s)
+    for i, (q, L) in enumerate(zip(seqs, lens)):
+        ref = plain.forward_logits(cfg.to_dict(), w, q, store=torch.bfloat16)
+        idx = list(wants[i]) + [L + t for t in range(3)]
+        assert rel_err(torch.stack(got[i]), ref[idx]) < TOL["bfloat16"]
