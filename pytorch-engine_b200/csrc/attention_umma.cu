@@ -6,18 +6,22 @@
 // A block owns 128 rows of one (sequence, kv head), a row being a (query token, head of the group)
 // pair, and walks the sequence's 64-key pages.  Roles:
 //   warp 5    TMA producer: Q once (a 3-D box [tokens][group heads][64 features] per feature half),
-//             then a K page and a V page per stage (2 stages);
+//             then K pages into a ring of two (a K page is spent as soon as S is there) and V pages
+//             into a ring of three (needed until P.V), each ring with barriers of its own, so that a
+//             page's copy starts two pages ahead;
 //   warp 4    MMA issuer: S = Q.K^T (128 x 64, eight k-steps of 16) into one of two S accumulators in
-//             tensor memory, and O += P.V (128 x 128, four k-steps of 16 keys) with V as an MN-major
-//             operand, so the page that TMA wrote as [keys][features] needs no transpose;
+//             tensor memory, and O += P.V (128 x 128, four k-steps of 16 keys) with P as the A operand
+//             from tensor memory and V as an MN-major operand from shared memory, so the page that TMA
+//             wrote as [keys][features] needs no transpose;
 //   warps 0-3 softmax: thread r owns row r.  It reads its S row from TMEM (tcgen05.ld), scales and
-//             masks, keeps the running maximum and sum in registers, writes P as bfloat16 in the
-//             swizzled K-major layout the MMA reads, into the shared memory of the page's K tile (which
-//             is spent once S is there, so P is double-buffered for free and the exponentials of one
-//             page overlap the P.V products of the page before), and rescales its O row in TMEM
-//             (tcgen05.ld / tcgen05.st) only when the maximum has grown by more than 2^8 since the last
-//             rescale (the reference of the exponentials is then moved; until then P simply carries
-//             the larger factor, which float32 sums and bfloat16 products hold without loss).
+//             masks (pages below the diagonal need no mask), keeps the running maximum and sum in
+//             registers, writes P as bfloat16 pairs back over the S columns it has read (tcgen05.st: P
+//             never touches shared memory), and rescales its O row in TMEM (tcgen05.ld / tcgen05.st)
+//             only when the maximum has grown by more than 2^8 since the last rescale (the reference of
+//             the exponentials is then moved; until then P simply carries the larger factor, which
+//             float32 sums and bfloat16 products hold without loss).
+// Products are executed in the order in which warp 4 issues them: S of page j + 2 overwrites the
+// columns of P of page j only after P.V of page j has read them.
 // S of the next page is computed while the softmax of the current one runs.  All waits are bounded.
 #include "common.cuh"
 #include "tma.cuh"
@@ -29,7 +33,8 @@ constexpr int HD = 128;        // head size
 constexpr int BM = 128;        // rows per block
 constexpr int BN = 64;         // keys per page
 constexpr int kQBytes = BM * HD * 2;          // 32 KB: two 64-feature halves of [128 rows][128 B]
-constexpr int kKVBytes = 2 * BN * HD * 2;     // 32 KB: K page then V page, each two halves of [64][128 B]
+constexpr int kPageBytes = BN * HD * 2;        // 16 KB: a K or V page, two halves of [64][128 B]
+constexpr int kKStages = 2, kVStages = 3;     // K is spent once S is there, V only after P.V: V needs the deeper ring
 constexpr int kTmemCols = 256;                // S0 [0,64) S1 [64,128) O [128,256)
 constexpr float kRescaleThreshold = 8.0f;     // in log2 units
 
@@ -63,6 +68,16 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
       "setp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
       "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// the same with the A operand read from tensor memory (row = lane, two bfloat16 per 32-bit column, so a
+// K = 16 step takes 8 columns)
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -128,16 +143,22 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
   pdl_wait();
   pdl_launch_dependents();
   char* q_s = smem;                       // [2 halves][128 rows][128 B]
-  char* kv_s = q_s + kQBytes;             // 2 stages of (K page, V page); P takes the K page's place once S is done
-  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + 2 * kKVBytes);
+  char* k_s = q_s + kQBytes;              // kKStages K pages
+  char* v_s = k_s + kKStages * kPageBytes;   // kVStages V pages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + kVStages * kPageBytes);
   uint64_t& q_full = bars[0];
-  uint64_t* kv_full = bars + 1;
-  uint64_t* kv_empty = bars + 3;
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_ready = bars + 7;   // one per stage: the softmax may be a page ahead of the P.V products
-  uint64_t& pv_done = bars[9];
-  uint32_t& tmem_holder = *reinterpret_cast<uint32_t*>(bars + 10);
-  volatile int& failed = *reinterpret_cast<volatile int*>(bars + 11);
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;    // [3]
+  uint64_t* v_empty = bars + 8;   // [3]
+  uint64_t* s_full = bars + 11;   // [2]
+  uint64_t* p_ready = bars + 13;  // [2]: one per S buffer, the softmax may be a page ahead of the P.V products
+  uint64_t& pv_done = bars[15];   // one phase per page: waited for only before O is rescaled
+  uint64_t& o_done = bars[16];    // the last P.V product is done.  (A barrier of its own: the softmax does not
+                                  // follow pv_done phase by phase, and a parity wait that is two phases
+                                  // ahead of the barrier passes at once.)
+  uint32_t& tmem_holder = *reinterpret_cast<uint32_t*>(bars + 17);
+  volatile int& failed = *reinterpret_cast<volatile int*>(bars + 18);
   if ((tma::smem_addr(smem) & 1023u) != 0) {   // the swizzled tiles need this alignment
     if (threadIdx.x == 0) report(a.status, kStatusWaitTimedOut, 29, (int)(tma::smem_addr(smem) & 1023u), 0);
     return;
@@ -161,13 +182,17 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
   if (tid == 0) {
     tma::mbar_init(&q_full, 1);
     for (int s = 0; s < 2; ++s) {
-      tma::mbar_init(&kv_full[s], 1);
-      tma::mbar_init(&kv_empty[s], 1);
+      tma::mbar_init(&k_full[s], 1);
+      tma::mbar_init(&k_empty[s], 1);
       tma::mbar_init(&s_full[s], 1);
+      tma::mbar_init(&p_ready[s], 128);
     }
-    tma::mbar_init(&p_ready[0], 128);
-    tma::mbar_init(&p_ready[1], 128);
+    for (int s = 0; s < kVStages; ++s) {
+      tma::mbar_init(&v_full[s], 1);
+      tma::mbar_init(&v_empty[s], 1);
+    }
     tma::mbar_init(&pv_done, 1);
+    tma::mbar_init(&o_done, 1);
     failed = 0;
     tma::fence_barrier_init();
   }
@@ -185,12 +210,6 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       load_3d(q_s, &qmap, 0, kvh * group, q0 + tok0, &q_full);
       load_3d(q_s + kQBytes / 2, &qmap, 64, kvh * group, q0 + tok0, &q_full);
       for (int j = 0; j < n_tiles && !failed; ++j) {
-        const int st = j & 1;
-        if (!tma::mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1)) {
-          report(a.status, kStatusWaitTimedOut, 20, blockIdx.x, j);
-          failed = 1;
-          break;
-        }
         const int k0 = k_begin + j * BN;
         const int logical = k0 / BN;
         int page = -1;
@@ -200,13 +219,25 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
           page = 0;
         }
         const int y = (page * a.n_kv_heads + kvh) * BN;
-        char* ks = kv_s + st * kKVBytes;
-        char* vs = ks + kKVBytes / 2;
-        tma::mbar_expect_tx(&kv_full[st], kKVBytes);
-        tma::load_2d(ks, &kmap, 0, y, &kv_full[st]);
-        tma::load_2d(ks + BN * 128, &kmap, 64, y, &kv_full[st]);
-        tma::load_2d(vs, &vmap, 0, y, &kv_full[st]);
-        tma::load_2d(vs + BN * 128, &vmap, 64, y, &kv_full[st]);
+        const int ks = j % kKStages, vs = j % kVStages;
+        if (!tma::mbar_wait(&k_empty[ks], ((j / kKStages) & 1) ^ 1)) {
+          report(a.status, kStatusWaitTimedOut, 20, blockIdx.x, j);
+          failed = 1;
+          break;
+        }
+        char* kd = k_s + ks * kPageBytes;
+        tma::mbar_expect_tx(&k_full[ks], kPageBytes);
+        tma::load_2d(kd, &kmap, 0, y, &k_full[ks]);
+        tma::load_2d(kd + BN * 128, &kmap, 64, y, &k_full[ks]);
+        if (!tma::mbar_wait(&v_empty[vs], ((j / kVStages) & 1) ^ 1)) {
+          report(a.status, kStatusWaitTimedOut, 24, blockIdx.x, j);
+          failed = 1;
+          break;
+        }
+        char* vd = v_s + vs * kPageBytes;
+        tma::mbar_expect_tx(&v_full[vs], kPageBytes);
+        tma::load_2d(vd, &vmap, 0, y, &v_full[vs]);
+        tma::load_2d(vd + BN * 128, &vmap, 64, y, &v_full[vs]);
       }
     }
   } else if (warp == 4) {
@@ -216,17 +247,18 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       const uint32_t idesc_pv = instr_desc(BM, HD, true);
       const uint32_t q_addr = tma::smem_addr(q_s);
       auto issue_qk = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!tma::mbar_wait(&kv_full[st], (j >> 1) & 1)) return false;
+        const int st = j & 1, ks = j % kKStages;
+        if (!tma::mbar_wait(&k_full[ks], (j / kKStages) & 1)) return false;
         fence_after_sync();
-        const uint32_t k_addr = tma::smem_addr(kv_s + st * kKVBytes);
+        const uint32_t k_addr = tma::smem_addr(k_s + ks * kPageBytes);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off_a = (k >> 2) * (BM * 128) + (k & 3) * 32;
           const uint32_t off_b = (k >> 2) * (BN * 128) + (k & 3) * 32;
           umma_bf16(tmem_base + st * BN, desc_k_major(q_addr + off_a), desc_k_major(k_addr + off_b), idesc_qk, k > 0 ? 1u : 0u);
         }
-        umma_commit(&s_full[st]);
+        umma_commit(&s_full[st]);     // S is there ...
+        umma_commit(&k_empty[ks]);    // ... and the K page is spent
         return true;
       };
       bool ok = tma::mbar_wait(&q_full, 0);
@@ -234,18 +266,20 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       for (int j = 0; ok && j < n_tiles; ++j) {
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);        // S of the next page while this one's softmax runs
         if (!ok) break;
-        const int st = j & 1;
+        const int st = j & 1, vs = j % kVStages;
         if (!tma::mbar_wait(&p_ready[st], (j >> 1) & 1)) { ok = false; break; }
+        if (!tma::mbar_wait(&v_full[vs], (j / kVStages) & 1)) { ok = false; break; }
         fence_after_sync();
-        const uint32_t p_addr = tma::smem_addr(kv_s + st * kKVBytes);   // where K of this page was
-        const uint32_t v_addr = p_addr + kKVBytes / 2;
+        const uint32_t p_tmem = tmem_base + st * BN;       // P lies where S of this page was (bfloat16 pairs, 32 columns)
+        const uint32_t v_addr = tma::smem_addr(v_s + vs * kPageBytes);
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k)
-          umma_bf16(tmem_o, desc_k_major(p_addr + k * 32), desc_mn_major(v_addr + k * 16 * 128, BN * 128), idesc_pv,
-                    (j > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&kv_empty[st]);
+          umma_bf16_a_tmem(tmem_o, p_tmem + k * 8, desc_mn_major(v_addr + k * 16 * 128, BN * 128), idesc_pv,
+                           (j > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&v_empty[vs]);
         umma_commit(&pv_done);
       }
+      if (ok) umma_commit(&o_done);
       if (!ok) {
         report(a.status, kStatusWaitTimedOut, 21, blockIdx.x, blockIdx.y);
         failed = 1;
@@ -275,11 +309,13 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
                          (a.window <= 0 || k0 > past + (row0 + BM - 1) / group - a.window);
       float mx = -INFINITY;
       if (whole) {
+        // four independent chains: a thread has few other warps to hide a 64-long dependent chain behind
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
-          for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sv[h][c]));
-        mx *= a.scale_log2;   // the scale is positive
+          for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(sv[h][c]));
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * a.scale_log2;   // the scale is positive
       } else {
 #pragma unroll
         for (int h = 0; h < 2; ++h)
@@ -314,24 +350,19 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       }
       if (grow) m_ref = mx;
       const float base = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float sum = 0.f;
-      char* prow = kv_s + st * kKVBytes + r * 128;   // K of this page is spent (S is done): P takes its place
-      // P = exp2(score - reference), as bfloat16 into the swizzled operand tile, 8 keys per 16-byte store
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};   // four chains (see the maximum); summed in a fixed order below
+      // P = exp2(score - reference) as bfloat16 pairs, back into tensor memory where S of this page was
+      // (this thread has read all of its S row): the P.V product takes its A operand from there
+      uint32_t pw[32];
       auto exps = [&](auto exponent) {
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
-          for (int c8 = 0; c8 < 4; ++c8) {
-            uint32_t w[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float p0 = fast_exp2(exponent(__uint_as_float(sv[h][c8 * 8 + 2 * i])));
-              const float p1 = fast_exp2(exponent(__uint_as_float(sv[h][c8 * 8 + 2 * i + 1])));
-              sum += p0 + p1;
-              w[i] = pack2(p0, p1);
-            }
-            const int chunk = h * 4 + c8;
-            *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          for (int c = 0; c < 16; ++c) {
+            const float p0 = fast_exp2(exponent(__uint_as_float(sv[h][2 * c])));
+            const float p1 = fast_exp2(exponent(__uint_as_float(sv[h][2 * c + 1])));
+            sum4[c & 3] += p0 + p1;
+            pw[h * 16 + c] = pack2(p0, p1);
           }
       };
       if (whole) {
@@ -340,12 +371,13 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       } else {
         exps([base](float s) { return s - base; });
       }
-      l += sum;
-      tma::fence_proxy_async();           // P must be visible to the tensor core's reads
+      tmem_st32(tmem_base + st * BN + lane_off, pw);
+      tmem_st_wait();
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       fence_before_sync();
       tma::mbar_arrive(&p_ready[st]);
     }
-    if (ok && tma::mbar_wait(&pv_done, (n_tiles - 1) & 1)) {
+    if (ok && tma::mbar_wait(&o_done, 0)) {
       fence_after_sync();
       const float inv = 1.f / fmaxf(l, 1e-20f);
       const int tok = row / group, head = kvh * group + row % group;
@@ -421,7 +453,7 @@ extern "C" int pe_attention_umma_prefill(const void* q, long long q_ld, long lon
   int me = pe::tma::make_map_2d_bf16(&kmap, k_pages, HD, rows, HD, 64, BN);
   if (me == 0) me = pe::tma::make_map_2d_bf16(&vmap, v_pages, HD, rows, HD, 64, BN);
   if (me != 0) return me < 0 ? me : PE_ERR_BAD_ARGUMENT;
-  const size_t smem = kQBytes + 2 * kKVBytes + 128;
+  const size_t smem = kQBytes + (kKStages + kVStages) * kPageBytes + 256;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t ce = cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -402,6 +402,37 @@ def test_attention_umma_prefill(ops, nh, nkv, window):
     assert rel_err(out.float().cpu().view(N, nh, d), want) < ATT_TOL[dtype]
 
 
+def test_attention_umma_prefill_blocks_of_two_pages_again_and_again(ops):
+    """Blocks that see two or three pages only (a short window) end a few barrier phases after they
+    start; a wait that names a phase by its parity must not pass because the barrier is two phases
+    behind.  The same launch forty times must give the same, right result every time."""
+    torch.manual_seed(27)
+    nh, nkv, d, dtype, window = 8, 4, 128, torch.bfloat16, 37
+    lens = [300, 77, 513, 130]
+    ps = PagedSetup(lens, nkv, d, dtype, seed=27, key_scale=2.0)
+    N = sum(lens)
+    q_all = torch.randn(N, nh * d + 2 * nkv * d, device=DEV).to(dtype)
+    qstart = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    past_t = torch.zeros(len(lens), dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    st = _status()
+    qs, o = [], 0
+    for n in lens:
+        qs.append(q_all[o:o + n, : nh * d].cpu().view(n, nh, d)); o += n
+    want = _plain_attention(ps, qs, [0] * len(lens), nh, scale, window)
+    outs = []
+    for _ in range(40):
+        out = torch.zeros(N, nh * d, device=DEV, dtype=dtype)
+        ops.attention_umma_prefill(q_all, out, len(lens), max(lens), nh, nkv, d, scale, window, qstart, past_t, ps.seq_slot,
+                                   ps.table, ps.num_pages, ps.k_pages, ps.v_pages, st)
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert st.tolist()[0] == 0
+    for out in outs:
+        assert torch.equal(out, outs[0])
+    assert rel_err(outs[0].float().cpu().view(N, nh, d), want) < ATT_TOL[dtype]
+
+
 def test_attention_umma_prefill_rescales_when_the_maximum_grows(ops):
     """Scores that grow by far more than 2^8 along the sequence: the reference of the exponentials
     must move and the accumulated output be rescaled."""
