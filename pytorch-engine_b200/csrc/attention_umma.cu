@@ -20,8 +20,8 @@
 //             only when the maximum has grown by more than 2^8 since the last rescale (the reference of
 //             the exponentials is then moved; until then P simply carries the larger factor, which
 //             float32 sums and bfloat16 products hold without loss).
-// Products are executed in the order in which warp 4 issues them: S of page j + 2 overwrites the
-// columns of P of page j only after P.V of page j has read them.
+// S of page j + 2 overwrites the columns of P of page j: warp 4 issues it only after P.V of page j
+// has completed.
 // S of the next page is computed while the softmax of the current one runs.  All waits are bounded.
 #include "common.cuh"
 #include "tma.cuh"
@@ -264,6 +264,10 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       bool ok = tma::mbar_wait(&q_full, 0);
       if (ok) ok = issue_qk(0);
       for (int j = 0; ok && j < n_tiles; ++j) {
+        // S of page j + 1 goes where P of page j - 1 lies: that P.V product must have read it.  (Products
+        // of one thread run in issue order on today's hardware; the wait makes the order explicit and
+        // costs nothing, the softmax of page j is still running.)
+        if (j >= 1 && j + 1 < n_tiles && !tma::mbar_wait(&pv_done, (j - 1) & 1)) { ok = false; break; }
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);        // S of the next page while this one's softmax runs
         if (!ok) break;
         const int st = j & 1, vs = j % kVStages;
