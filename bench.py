@@ -8,9 +8,9 @@ A step is one decode step: every live sequence gets one token (model step + samp
 run has the layer sizes of the Qwen3-8B shape, a batch of 8 and a context of 4,096.  One JSON line
 is printed: ``value`` is decoded tokens/s timed on the device with CUDA events; ``e2e`` is the same
 through the Python entry point (``Engine.stream_tokens``: host token ids in, host token ids out
-every step); ``prefill`` is one 2,048-token prompt; ``roofline`` is the bytes a decode step must
-read (every weight once, the cache of the live requests) over its time; ``points`` holds decode at
-batch 1 and 64.  For the device-timed decode numbers the cache is brought to the wanted length by
+every step; W untimed decode steps after the prompts, then K timed ones); ``prefill`` is one
+2,048-token prompt; ``roofline`` is the bytes a decode step must read (every weight once, the cache
+of the live requests) over its time; ``points`` holds decode at batch 1 and 64.  For the device-timed decode numbers the cache is brought to the wanted length by
 reserving pages over storage filled with random values (what a decode step costs does not depend
 on the values); the end-to-end number runs real prompts through the public API.
 """
@@ -275,27 +275,27 @@ def main():
         out["points"] = pts
 
     if not args.no_e2e:
-        # through the public API: real prompts, host token ids in and out at every step
+        # through the public API: real prompts, host token ids in and out at every step; W untimed
+        # decode steps after the prompts, then K timed ones
         steps_e = max(8, K)
-        plen = ctx - steps_e - 1
+        plen = ctx - steps_e - W - 1
         prompts = [torch.randint(0, vocab, (plen,), generator=gen).tolist() for _ in range(B)]
-        params = pe.SamplingParams.greedy_params(max_tokens=steps_e + 1)
+        params = pe.SamplingParams.greedy_params(max_tokens=steps_e + W + 1)
         t_first = None
         n_tokens = 0
+        got = [0] * B
         for chunk in engine.stream_tokens(prompts, params):
+            got[chunk.request] += 1
             if t_first is None:
-                torch.cuda.synchronize()
-                t_first = time.perf_counter()
-                seen_first = set()
-            if chunk.request in seen_first:
-                n_tokens += 1
+                if min(got) >= W + 1:           # every request has its first token and W decoded ones: from
+                    t_first = time.perf_counter()   # this delivery to the last one lie exactly K steps
             else:
-                seen_first.add(chunk.request)
+                n_tokens += 1
         torch.cuda.synchronize()
         dt = time.perf_counter() - t_first
         out["e2e"] = {"value": round(n_tokens / dt, 2), "unit": "tokens/s", "tokens": n_tokens,
                       "h2d_bytes_per_step": (B + 3 * B + 1 + B) * 4 + 2 * B * 4, "d2h_bytes_per_step": B * 4 + 16,
-                      "api": "Engine.stream_tokens, greedy, prompts of %d tokens" % plen}
+                      "api": "Engine.stream_tokens, greedy, prompts of %d tokens, %d untimed steps" % (plen, W)}
 
     print(json.dumps(out))
     return 0
