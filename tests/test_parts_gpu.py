@@ -1,5 +1,6 @@
 """Each part alone against its plain formula, and toy architectures whose parts are defined here (a
-mixer that keeps state of its own, a feed-forward with routing, another position encoding):
+mixer that keeps state of its own, a feed-forward with routing, another position encoding, another
+block arrangement):
 registered, built and stepped from the test, with no change to the package's files."""
 import math
 from dataclasses import dataclass
@@ -510,3 +511,78 @@ def test_toy_routed_feed_forward_and_another_position_encoding(pe):
         pe.parts.unregister("feed_forward", "top_one_experts")
         pe.parts.unregister("position", "slow_rope")
         pe.config.unregister_architecture("ToyRoutedLM")
+
+
+# ---- a toy block arrangement ------------------------------------------------------------------------------
+class ParallelBlock:
+    """``out = x + mixer(norm(x)) + ffn(norm(x))``: mixer and feed-forward read the same normed input
+    (the second norm of the block's description is built but not used)."""
+
+    graph_safe = True
+
+    def __init__(self, spec, parts, runtime):
+        self.rt, self.norm, self.mixer, self.ffn = runtime, parts["mixer_norm"], parts["mixer"], parts["ffn"]
+
+    def forward(self, stream, pending, ctx, view, writes_cache=True):
+        normed = ctx.buffer("parallel.normed", tuple(stream.shape), self.rt.dtype)
+        self.norm.add_forward(stream, pending, normed)            # adds the block before's delta, then norms
+        mixed = self.mixer.forward(normed, ctx, view)
+        return (mixed.float() + self.ffn.forward(normed, ctx).float()).to(self.rt.dtype)
+
+
+def test_toy_block_arrangement(pe):
+    """An arrangement defined here is registered and chosen for one block of a model whose other block
+    keeps the package's pre-norm arrangement."""
+    P, B, R = pe.parts.PartSpec, pe.parts.BlockSpec, pe.parts.RunStep
+    eps, theta = 1e-6, 10000.0
+    cfg = ToyMixConfig(hidden_size=48, vocab_size=101, heads=3, kv_heads=3, head_dim=16, architecture="ToyParallelLM")
+
+    def plan(c):
+        h, d = c.hidden_size, c.head_dim
+        norm = lambda n: P("rmsnorm", {"dim": h, "eps": eps}, {"weight": n})
+        att = lambda i: P("attention", {"hidden": h, "n_heads": c.heads, "n_kv_heads": c.kv_heads, "head_dim": d,
+                                        "qk_norm": False, "eps": eps, "scale": None, "window": None, "position": "rope"},
+                          {k: f"l{i}.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj")})
+        ffn = lambda i: P("swiglu", {"hidden": h, "intermediate": 2 * h}, {"gate_proj": f"l{i}.g", "up_proj": f"l{i}.u", "down_proj": f"l{i}.d"})
+        blocks = (B("parallel", norm("l0.n1"), att(0), norm("l0.n2"), ffn(0), name="parallel"),
+                  B("pre_norm", norm("l1.n1"), att(1), norm("l1.n2"), ffn(1), name="sequential"))
+        return pe.parts.ModelPlan(
+            hidden_size=h, vocab_size=c.vocab_size, max_positions=c.max_position_embeddings,
+            embedding=P("token_embedding", {"vocab": c.vocab_size, "hidden": h}, {"weight": "emb"}),
+            blocks=blocks, order=(R(0), R(1)), final_norm=norm("fn"),
+            head=P("linear_head", {"vocab": c.vocab_size, "hidden": h}, {"weight": "emb"}),
+            positions={"rope": P("rope", {"rotary_dim": d, "theta": theta, "max_positions": c.max_position_embeddings})})
+
+    pe.parts.register("arrangement", "parallel", ParallelBlock, replace=True)
+    pe.register_architecture("ToyParallelLM", ToyMixConfig, plan, replace=True)
+    try:
+        eng = pe.Engine.from_random(cfg, seed=12, dtype="float32", max_cache_tokens=256, max_batch=2)
+        w = {k: v.float().cpu() for k, v in pe.weights.random_weights(eng.plan, 12, device=DEV).items()}
+        nH, d = cfg.heads, cfg.head_dim
+
+        def attention(x, i):
+            S = x.shape[0]
+            cos, sin = plain.rope_cos_sin(torch.arange(S), d, theta)
+            q = plain.rope_rotate_neox((x @ w[f"l{i}.q_proj"].T).view(S, nH, d), cos, sin, d)
+            k = plain.rope_rotate_neox((x @ w[f"l{i}.k_proj"].T).view(S, nH, d), cos, sin, d)
+            v = (x @ w[f"l{i}.v_proj"].T).view(S, nH, d)
+            return plain.causal_gqa_attention(q, k, v, d ** -0.5).reshape(S, nH * d) @ w[f"l{i}.o_proj"].T
+
+        def plain_toy(tokens):
+            x = w["emb"][tokens]
+            n = plain.rms_norm(x, w["l0.n1"], eps)
+            x = x + attention(n, 0) + plain.swiglu(n, w["l0.g"], w["l0.u"], w["l0.d"])
+            x = x + attention(plain.rms_norm(x, w["l1.n1"], eps), 1)
+            x = x + plain.swiglu(plain.rms_norm(x, w["l1.n2"], eps), w["l1.g"], w["l1.u"], w["l1.d"])
+            return plain.rms_norm(x, w["fn"], eps) @ w["emb"].T
+
+        toks = [5, 9, 2, 77, 31, 8, 8, 40, 3, 61, 100]
+        s = eng.alloc_slot()
+        lg = [eng.step([pe.StepEntry(s, toks[:7], (0, 6))]).cpu()]
+        for t in toks[7:]:
+            lg.append(eng.step([pe.StepEntry(s, [t], (0,))]).cpu())
+        eng.free_slot(s)
+        assert rel_err(torch.cat(lg), plain_toy(toks)[[0, 6, 7, 8, 9, 10]]) < 1e-5
+    finally:
+        pe.parts.unregister("arrangement", "parallel")
+        pe.config.unregister_architecture("ToyParallelLM")
