@@ -1,6 +1,6 @@
 """Each part alone against its plain formula, and toy architectures whose parts are defined here (a
 mixer that keeps state of its own, a feed-forward with routing, another position encoding, another
-block arrangement):
+block arrangement, another norm):
 registered, built and stepped from the test, with no change to the package's files."""
 import math
 from dataclasses import dataclass
@@ -586,3 +586,96 @@ def test_toy_block_arrangement(pe):
     finally:
         pe.parts.unregister("arrangement", "parallel")
         pe.config.unregister_architecture("ToyParallelLM")
+
+
+# ---- a toy norm ----------------------------------------------------------------------------------------------
+class CenteredNorm:
+    """LayerNorm without bias: ``(x - mean) / sqrt(var + eps) * weight``, statistics in float32."""
+
+    graph_safe = True
+
+    @classmethod
+    def weight_decls(cls, params):
+        from importlib import import_module
+        WeightDecl = import_module("pytorch-engine_b200").parts.WeightDecl
+        return {"weight": WeightDecl((int(params["dim"]),), "norm")}
+
+    def __init__(self, params, weights, runtime):
+        self.eps = float(params["eps"])
+        self.weight = runtime.adopt(weights["weight"], torch.float32)
+
+    def _norm(self, x):
+        x = x.float()
+        x = x - x.mean(-1, keepdim=True)
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight
+
+    def add_forward(self, residual, delta, out, rows=None):
+        if delta is not None:
+            residual.add_(delta.float())          # the stream takes the pending delta, as the package's norm does
+        src = residual if rows is None else residual[rows.long()]
+        out.copy_(self._norm(src).to(out.dtype))
+        return out
+
+    def forward(self, x, out=None):
+        y = self._norm(x).to(x.dtype)
+        return y if out is None else out.copy_(y)
+
+
+def test_toy_norm(pe):
+    """A norm defined here takes the place of every norm of a small model (final norm included)."""
+    P, B, R = pe.parts.PartSpec, pe.parts.BlockSpec, pe.parts.RunStep
+    eps, theta = 1e-5, 10000.0
+    cfg = ToyMixConfig(hidden_size=40, vocab_size=89, heads=2, kv_heads=1, head_dim=16, architecture="ToyCenteredLM")
+
+    def plan(c):
+        h, d = c.hidden_size, c.head_dim
+        norm = lambda n: P("centered", {"dim": h, "eps": eps}, {"weight": n})
+        att = P("attention", {"hidden": h, "n_heads": c.heads, "n_kv_heads": c.kv_heads, "head_dim": d, "qk_norm": False,
+                              "eps": eps, "scale": None, "window": None, "position": "rope"},
+                {k: f"l0.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj")})
+        ffn = P("swiglu", {"hidden": h, "intermediate": 64}, {"gate_proj": "l0.g", "up_proj": "l0.u", "down_proj": "l0.d"})
+        return pe.parts.ModelPlan(
+            hidden_size=h, vocab_size=c.vocab_size, max_positions=c.max_position_embeddings,
+            embedding=P("token_embedding", {"vocab": c.vocab_size, "hidden": h}, {"weight": "emb"}),
+            blocks=(B("pre_norm", norm("l0.n1"), att, norm("l0.n2"), ffn, name="only"),), order=(R(0),),
+            final_norm=norm("fn"), head=P("linear_head", {"vocab": c.vocab_size, "hidden": h}, {"weight": "head"}),
+            positions={"rope": P("rope", {"rotary_dim": d, "theta": theta, "max_positions": c.max_position_embeddings})})
+
+    pe.parts.register("norm", "centered", CenteredNorm, replace=True)
+    pe.register_architecture("ToyCenteredLM", ToyMixConfig, plan, replace=True)
+    try:
+        eng = pe.Engine.from_random(cfg, seed=13, dtype="float32", max_cache_tokens=128, max_batch=2)
+        w = {k: v.float().cpu() for k, v in pe.weights.random_weights(eng.plan, 13, device=DEV).items()}
+        nH, nKV, d = cfg.heads, cfg.kv_heads, cfg.head_dim
+
+        def cnorm(x, weight):
+            x = x - x.mean(-1, keepdim=True)
+            return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight
+
+        def plain_toy(tokens):
+            x = w["emb"][tokens]
+            S = len(tokens)
+            n = cnorm(x, w["l0.n1"])
+            cos, sin = plain.rope_cos_sin(torch.arange(S), d, theta)
+            q = plain.rope_rotate_neox((n @ w["l0.q_proj"].T).view(S, nH, d), cos, sin, d)
+            k = plain.rope_rotate_neox((n @ w["l0.k_proj"].T).view(S, nKV, d), cos, sin, d)
+            v = (n @ w["l0.v_proj"].T).view(S, nKV, d)
+            x = x + plain.causal_gqa_attention(q, k, v, d ** -0.5).reshape(S, nH * d) @ w["l0.o_proj"].T
+            x = x + plain.swiglu(cnorm(x, w["l0.n2"]), w["l0.g"], w["l0.u"], w["l0.d"])
+            return cnorm(x, w["fn"]) @ w["head"].T
+
+        seqs = [[5, 9, 2, 77, 31, 8, 8, 40], [88, 0, 3]]
+        slots = [eng.alloc_slot(), eng.alloc_slot()]
+        lg = eng.step([pe.StepEntry(slots[0], seqs[0][:6], (2, 5)), pe.StepEntry(slots[1], seqs[1][:2], (1,))]).cpu()
+        got0, got1 = [lg[0], lg[1]], [lg[2]]
+        lg = eng.step([pe.StepEntry(slots[0], [seqs[0][6]], (0,)), pe.StepEntry(slots[1], [seqs[1][2]], (0,))]).cpu()
+        got0.append(lg[0]); got1.append(lg[1])
+        lg = eng.step([pe.StepEntry(slots[0], [seqs[0][7]], (0,))]).cpu()
+        got0.append(lg[0])
+        for s in slots:
+            eng.free_slot(s)
+        assert rel_err(torch.stack(got0), plain_toy(seqs[0])[[2, 5, 6, 7]]) < 1e-5
+        assert rel_err(torch.stack(got1), plain_toy(seqs[1])[[1, 2]]) < 1e-5
+    finally:
+        pe.parts.unregister("norm", "centered")
+        pe.config.unregister_architecture("ToyCenteredLM")
