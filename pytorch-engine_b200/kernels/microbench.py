@@ -2,8 +2,10 @@
 
 Each case is timed with CUDA events on the launching stream after warm-up.  Cases that compare
 kernels call them in turn inside one loop, so that all see the same clocks, and flush L2 between
-calls by writing a 256 MB buffer (the matrix products, the decode attention) or time a run of calls
-in a row (the sampler, whose logits come out of the preceding kernel and sit in L2).
+calls by reading a 256 MB buffer (the matrix products, the decode attention; reading, because a
+written buffer leaves 126 MB of dirty lines whose write-back then competes with the timed kernel's
+reads: that cost a 201 MB weight stream 20 us) or time a run of calls in a row (the sampler, whose
+logits come out of the preceding kernel and sit in L2).
 """
 from __future__ import annotations
 
@@ -16,7 +18,12 @@ from . import ops
 
 
 def _flush_buffer(device) -> torch.Tensor:
-    return torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    return torch.zeros(64 << 20, dtype=torch.int32, device=device)   # 256 MB
+
+
+def _flush(buffer: torch.Tensor) -> None:
+    """Fill L2 with clean lines of ``buffer``."""
+    buffer.sum()
 
 
 def time_in_turn(fns: Sequence[Callable[[], None]], flush: torch.Tensor, rounds: int = 15) -> List[float]:
@@ -27,7 +34,7 @@ def time_in_turn(fns: Sequence[Callable[[], None]], flush: torch.Tensor, rounds:
     times: List[List[float]] = [[] for _ in fns]
     for _ in range(rounds):
         for i, f in enumerate(fns):
-            flush.zero_()
+            _flush(flush)
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             f()
