@@ -1,10 +1,11 @@
 // Prefill attention on the fifth-generation tensor cores (tcgen05.mma), for bfloat16, head size 128
-// and groups of 1, 2, 4, 8 or 16 query heads per kv head.  Same contract and formulas as
+// and groups of up to 32 query heads per kv head.  Same contract and formulas as
 // attention_mma.cu (pygguf_engine/kv_cache.py:833, 2189-2192 masks; 756 head mapping; 836-861 online
 // softmax); other shapes keep using that file.
 //
-// A block owns 128 rows of one (sequence, kv head), a row being a (query token, head of the group)
-// pair, and walks the sequence's 64-key pages.  Roles:
+// A block owns up to 128 rows of one (sequence, kv head), a row being a (query token, head of the
+// group) pair: 128 / group whole tokens (a group of 5 gives 125 rows; the rest of the MMA's 128 rows is
+// zero and is never stored).  It walks the sequence's 64-key pages.  Roles:
 //   warp 5    TMA producer: Q once (a 3-D box [tokens][group heads][64 features] per feature half),
 //             then K pages into a ring of two (a K page is spent as soon as S is there) and V pages
 //             into a ring of three (needed until P.V), each ring with barriers of its own, so that a
@@ -168,11 +169,12 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
   const int group = a.group;
   const int q0 = a.seq_qstart[b], q_len = a.seq_qstart[b + 1] - q0, past = a.seq_past[b];
   const int n_rows = q_len * group;
-  const int row0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BM;
+  const int rows_blk = (BM / group) * group;                  // whole tokens only
+  const int row0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * rows_blk;
   if (row0 >= n_rows) return;
   const int slot = a.seq_slot[b];
-  const int tok0 = row0 / group;                              // BM is a multiple of the group
-  const int last_row = min(n_rows, row0 + BM) - 1;
+  const int tok0 = row0 / group;
+  const int last_row = min(n_rows, row0 + rows_blk) - 1;
   const int first_pos = past + tok0, last_pos = past + last_row / group;
   int k_begin = 0;
   if (a.window > 0) k_begin = max(0, first_pos - a.window + 1) / BN * BN;
@@ -196,6 +198,13 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
     failed = 0;
     tma::fence_barrier_init();
   }
+  // the Q rows beyond the block's whole tokens are no copy's target: zero them (both feature halves)
+  // so that the MMA's rows there stay finite; they are never stored
+  for (int i = tid; i < (BM - rows_blk) * 2 * 8; i += blockDim.x) {
+    const int rr = rows_blk + i / 16, half = (i / 8) & 1, chunk = i & 7;
+    *reinterpret_cast<uint4*>(q_s + half * (kQBytes / 2) + rr * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
+  }
+  tma::fence_proxy_async();
   if (warp == 4) tmem_alloc(&tmem_holder, kTmemCols);
   fence_before_sync();
   __syncthreads();
@@ -206,7 +215,7 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
   if (warp == 5) {
     // ---- TMA producer ----
     if (lane == 0) {
-      tma::mbar_expect_tx(&q_full, kQBytes);
+      tma::mbar_expect_tx(&q_full, (uint32_t)(rows_blk * HD * 2));
       load_3d(q_s, &qmap, 0, kvh * group, q0 + tok0, &q_full);
       load_3d(q_s + kQBytes / 2, &qmap, 64, kvh * group, q0 + tok0, &q_full);
       for (int j = 0; j < n_tiles && !failed; ++j) {
@@ -293,7 +302,7 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
     // ---- softmax: thread r owns row r ----
     const int r = tid;                               // 0..127; warp w reads TMEM lanes 32w..32w+31
     const int row = row0 + r;
-    const bool live = row < n_rows;
+    const bool live = r < rows_blk && row < n_rows;
     const int qpos = past + row / group;
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
     float m_ref = -INFINITY, l = 0.f;
@@ -309,8 +318,8 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       tmem_ld_wait();
       // A page that every row of this block sees whole (below the diagonal, inside the window) needs
       // no mask: the scores stay raw and the scale is folded into the exponent's multiply-add.
-      const bool whole = a.scale_log2 > 0.f && (row0 + BM <= n_rows) && (k0 + BN - 1 <= past + row0 / group) &&
-                         (a.window <= 0 || k0 > past + (row0 + BM - 1) / group - a.window);
+      const bool whole = a.scale_log2 > 0.f && (row0 + rows_blk <= n_rows) && (k0 + BN - 1 <= past + row0 / group) &&
+                         (a.window <= 0 || k0 > past + (row0 + rows_blk - 1) / group - a.window);
       float mx = -INFINITY;
       if (whole) {
         // four independent chains: a thread has few other warps to hide a 64-long dependent chain behind
@@ -422,7 +431,7 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
 extern "C" int pe_attention_umma_supported(int head_dim, int n_heads, int n_kv_heads) {
   if (head_dim != 128 || n_kv_heads <= 0 || n_heads % n_kv_heads) return 0;
   const int g = n_heads / n_kv_heads;
-  return (g == 1 || g == 2 || g == 4 || g == 8 || g == 16) ? 1 : 0;
+  return (g >= 1 && g <= 32) ? 1 : 0;
 }
 
 // Prefill form only (decode keeps attention_mma.cu).  q: rows of the fused q|k|v buffer, [n_tokens, q_ld].
@@ -464,7 +473,8 @@ extern "C" int pe_attention_umma_prefill(const void* q, long long q_ld, long lon
     if (ce != cudaSuccess) return (int)ce;
     attr_set = true;
   }
-  const long long tiles = ((long long)max_q * a.group + BM - 1) / BM;
+  const int rows_blk = (BM / a.group) * a.group;
+  const long long tiles = ((long long)max_q * a.group + rows_blk - 1) / rows_blk;
   dim3 grid((unsigned)tiles, n_kv_heads, n_seqs);
   if (grid.y > 65535 || grid.z > 65535) return PE_ERR_UNSUPPORTED_SIZE;
   pe::launch(prefill_umma_kernel, grid, 192, smem, stream, a, qmap, kmap, vmap);

@@ -272,7 +272,7 @@ def attention_umma_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_
                            head_dim: int, scale: float, window: int, seq_qstart: torch.Tensor, seq_past: torch.Tensor,
                            seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int, k_pages: torch.Tensor,
                            v_pages: torch.Tensor, status: torch.Tensor) -> None:
-    """Prefill attention on tcgen05 (bfloat16, head size 128, group 1/2/4/8/16); ``q`` holds the step's
+    """Prefill attention on tcgen05 (bfloat16, head size 128, groups up to 32); ``q`` holds the step's
     query rows (the first ``n_heads * head_dim`` features of each row of the fused q|k|v buffer)."""
     _need(q.stride(-1) == 1 and out.stride(-1) == 1, "attention: rows must be contiguous")
     _need(q.dtype == out.dtype == k_pages.dtype == torch.bfloat16, "attention_umma: bfloat16 tensors only")

@@ -372,10 +372,11 @@ def test_attention_mma_prefill(ops, nh, nkv, d, window):
     assert rel_err(out.float().cpu().view(N, nh, d), want) < ATT_TOL[dtype]
 
 
-@pytest.mark.parametrize("nh,nkv", [(32, 8), (16, 1), (3, 3), (8, 4), (16, 2)])
+@pytest.mark.parametrize("nh,nkv", [(32, 8), (16, 1), (3, 3), (8, 4), (16, 2), (10, 2), (6, 2), (3, 1), (24, 1)])
 @pytest.mark.parametrize("window", [0, 37, 150])
 def test_attention_umma_prefill(ops, nh, nkv, window):
-    """The tcgen05 prefill attention against the plain formula (head size 128, groups 4, 16, 1, 2, 8)."""
+    """The tcgen05 prefill attention against the plain formula (head size 128; groups 4, 16, 1, 2, 8, and
+    5, 3, 24, which do not divide a block's 128 rows)."""
     torch.manual_seed(25)
     d, dtype = 128, torch.bfloat16
     assert ops.attention_umma_supported(dtype, d, nh, nkv)

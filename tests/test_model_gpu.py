@@ -384,7 +384,7 @@ def test_trace_run_program(pe, model_folders, oracles, tmp_path, dtype):
 
 
 @pytest.mark.parametrize("hidden,inter,heads,kv,d,window", [(256, 384, 4, 2, 128, None), (200, 328, 6, 2, 64, 300),
-                                                           (320, 640, 2, 1, 128, 700)])
+                                                           (320, 640, 2, 1, 128, 700), (192, 256, 5, 1, 128, None)])
 def test_a_prompt_of_more_than_a_thousand_tokens(pe, hidden, inter, heads, kv, d, window):
     """Prompts this long take the many-row kernels (the tcgen05 products where K is a multiple of 64,
     the tcgen05 attention at head size 128): a long and a short prompt in one step, then single tokens,
