@@ -82,7 +82,7 @@ class GQAttention:
         # the generic float32-arithmetic kernels otherwise
         self.use_mma = runtime.is_cuda and ops.attention_mma_supported(runtime.dtype, self.head_dim, self.n_heads,
                                                                        self.n_kv_heads)
-        # prefill on tcgen05 where that kernel takes the shape (bfloat16, head size 128, group 1/2/4/8/16)
+        # prefill on tcgen05 where that kernel takes the shape (bfloat16, head size 128, groups up to 32)
         self.use_umma_prefill = runtime.is_cuda and ops.attention_umma_supported(runtime.dtype, self.head_dim,
                                                                                   self.n_heads, self.n_kv_heads)
 
