@@ -245,22 +245,28 @@ def gemm_umma2(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, status:
     _count(1)
 
 
-def attention_mma_decode_ranges(device: torch.device, head_dim: int, n_seqs: int, n_kv_heads: int, max_kv_len: int,
-                                split_keys: int) -> tuple:
-    """(split_keys, max_splits) for the tensor-core decode attention; split_keys 0 means that each
-    sequence's keys are shared out evenly over max_splits ranges (in whole pages).  When one wave of
-    blocks can hold at least two ranges per (sequence, kv head), that many ranges are used, but not
-    more than ranges of ``split_keys`` keys would give (measured: the blocks of a second, partly filled
-    wave cost more than longer ranges do, and more, shorter ranges only add merge work).  With more
-    pairs than that there are several waves anyway, and ranges of about four times ``split_keys``
-    keys were measured best (batch 64 at 4,096 keys: 169 us with two ranges, 179 us with eight)."""
-    slots = sm_count(device) * int(library().pe_attention_mma_decode_blocks_per_sm(head_dim))
-    pairs = max(1, n_seqs * n_kv_heads)
+def decode_ranges(slots: int, pairs: int, max_kv_len: int, split_keys: int) -> tuple:
+    """(split_keys, max_splits) for a decode attention whose SMs hold ``slots`` blocks at a time and that
+    has ``pairs`` (sequence, kv head) pairs; split_keys 0 means that each sequence's keys are shared
+    out evenly over max_splits ranges (in whole pages).  When one wave of blocks can hold at least two
+    ranges per pair, that many ranges are used, but not more than ranges of ``split_keys`` keys would
+    give (measured: the blocks of a second, partly filled wave cost more than longer ranges do, and
+    more, shorter ranges only add merge work).  With more pairs than that there are several waves
+    anyway, and ranges of about four times ``split_keys`` keys were measured best (batch 64 at 4,096
+    keys: 169 us with two ranges, 179 us with eight)."""
+    pairs = max(1, pairs)
     fixed = max(1, -(-max_kv_len // split_keys))
     per_pair = slots // pairs
     if per_pair < 2:
         return 0, max(1, min(fixed, -(-max_kv_len // (4 * split_keys))))
     return 0, min(per_pair, fixed)
+
+
+def attention_mma_decode_ranges(device: torch.device, head_dim: int, n_seqs: int, n_kv_heads: int, max_kv_len: int,
+                                split_keys: int) -> tuple:
+    """``decode_ranges`` for csrc/attention_mma.cu on this device."""
+    slots = sm_count(device) * int(library().pe_attention_mma_decode_blocks_per_sm(head_dim))
+    return decode_ranges(slots, n_seqs * n_kv_heads, max_kv_len, split_keys)
 
 
 def attention_umma_supported(dtype: torch.dtype, head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
