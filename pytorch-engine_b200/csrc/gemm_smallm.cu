@@ -55,7 +55,7 @@ template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat
 // (gate and up), combined as silu(gate) * up.  WARPS: warps per block = K slices.  U: k blocks per batch
 // of loads.
 // Registers are capped at 128 per thread for M <= 8 so that 16 warps fit on an SM: what limits this
-// kernel is how many bytes its SM has in flight.
+// kernel is how many bytes its SM has in flight.  For M <= 16 that cap would spill.
 template <int NT, bool PAIR, int WARPS, int U, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32, NT == 1 ? 16 / WARPS : 1) gemm_smallm_kernel(Args a) {
   __shared__ float red[WARPS][(PAIR ? 2 : 1) * NT][4][32];
@@ -191,10 +191,17 @@ static int launch(const Args& a, cudaStream_t stream) {
   const int kblocks = (a.K + 31) / 32;
   constexpr int U = PAIR ? 2 : 4;
   // K slices per block of 16 weight rows: enough warps in flight over the whole GPU to cover the
-  // memory latency (about 24 per SM), but at least two batches of k blocks per warp.
+  // memory latency, but at least two batches of k blocks per warp.  An SM holds 16 warps of the
+  // M <= 8 kernels (128 registers) and 12 of the M <= 16 kernels (up to 168 registers) as long as their
+  // blocks have at most 4 warps; a block of 8 would be alone on its SM.
+  constexpr int kMaxWarps = NT == 1 ? 8 : 4;
+  const long long slots = 148LL * (NT == 1 ? 16 : 12);
   const long long want_warps = 148LL * 24;
   int warps = 1;
-  while (warps < 8 && (long long)blocks * warps < want_warps && kblocks / (warps * 2) >= 2 * U) warps *= 2;
+  while (warps < kMaxWarps && (long long)blocks * warps < want_warps && kblocks / (warps * 2) >= 2 * U) warps *= 2;
+  // A second wave that fills less than half of the GPU costs more than longer K slices in one wave
+  // (6144 x 4096 at 8 rows: 11.5 us with 8 warps a block, 1.3 waves; 10.2 us with 4).
+  if (warps > 1 && (long long)blocks * warps > slots && (long long)blocks * warps * 2 <= slots * 3) warps /= 2;
   switch (warps) {
     case 1: pe::launch(gemm_smallm_kernel<NT, PAIR, 1, U, OutT>, blocks, 32, 0, stream, a); break;
     case 2: pe::launch(gemm_smallm_kernel<NT, PAIR, 2, U, OutT>, blocks, 64, 0, stream, a); break;
