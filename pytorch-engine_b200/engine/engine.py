@@ -187,9 +187,20 @@ class Engine:
     def stream_tokens(self, prompt_or_ids, sampling: Optional[SamplingParams] = None) -> Iterator[StreamChunk]:
         prompts, _ = self._as_batch(prompt_or_ids)
         # no_grad rather than inference_mode: buffers made here are also written by later calls of
-        # step(), which may come from outside any such context
-        with torch.no_grad():
-            yield from self.loop.stream(prompts, sampling)
+        # step(), which may come from outside any such context.  It is entered for each advance of the
+        # loop and left before the chunk is handed out, so the caller's own code between two chunks
+        # runs in the caller's grad mode.
+        chunks = self.loop.stream(prompts, sampling)
+        try:
+            while True:
+                with torch.no_grad():
+                    try:
+                        chunk = next(chunks)
+                    except StopIteration:
+                        return
+                yield chunk
+        finally:
+            chunks.close()
 
     # ---- reports -----------------------------------------------------------------------------
     def memory_report(self) -> Dict[str, float]:

@@ -64,9 +64,9 @@ class ModelRunner:
             if len(e.tokens) == 0:
                 raise ValueError(f"slot {e.slot} brings no token in this step")
             pasts.append(self.cache.length(e.slot))
-        # make room first: on a failure the pages taken so far go back and the cache is as it was
+        ints, n_tokens, n_want = StepContext.pack_meta(entries, pasts)   # raises on a wanted place outside the step
+        # make room before anything runs: on a failure the pages taken so far go back and the cache is as it was
         self._reserve_all([(e.slot, past + len(e.tokens)) for e, past in zip(entries, pasts)])
-        ints, n_tokens, n_want = StepContext.pack_meta(entries, pasts)
         n_seqs = len(entries)
         q_lens = [len(e.tokens) for e in entries]
         decode = all(q == 1 for q in q_lens)
