@@ -303,6 +303,25 @@ def test_generate_and_step_share_an_engine(pe, engines, oracles):
     assert [r.token_ids for r in again] == [r.token_ids for r in first]
 
 
+def test_streaming_leaves_the_callers_grad_mode_alone_and_frees_slots_when_abandoned(pe, engines, oracles):
+    cfg, w = oracles["A"]
+    eng = engines("A", "float32")
+    prompts = [_tokens(cfg["vocab_size"], n, 90 + n) for n in (5, 9)]
+    whole = eng.generate(prompts, pe.SamplingParams.greedy_params(max_tokens=6))
+    got = {0: [], 1: []}
+    for chunk in eng.stream_tokens(prompts, pe.SamplingParams.greedy_params(max_tokens=6)):
+        assert torch.is_grad_enabled()           # between two chunks the caller's code runs in the caller's mode
+        got[chunk.request].append(chunk.token_id)
+    assert [got[0], got[1]] == [r.token_ids for r in whole]
+    stream = eng.stream_tokens(prompts, pe.SamplingParams.greedy_params(max_tokens=6))
+    next(stream)
+    stream.close()                               # given up in mid-batch: the slots and pages come back
+    assert eng.cache.live_slots == []
+    eng.cache.check()
+    assert [r.token_ids for r in eng.generate(prompts, pe.SamplingParams.greedy_params(max_tokens=6))] == \
+        [r.token_ids for r in whole]
+
+
 def test_stop_token_and_context_limit(pe, engines, oracles):
     cfg, w = oracles["A"]
     eng = engines("A", "float32")
