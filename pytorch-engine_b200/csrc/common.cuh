@@ -42,7 +42,9 @@ __device__ __forceinline__ void report(int* status, int code, int a = 0, int b =
 // loop is done).  So at most one successor is resident and waiting at any time: letting successors
 // start earlier was measured to cost more (their waiting blocks take registers and warp slots from
 // the kernel that is running) than it gains.  Nothing is read from, or written to, memory that
-// another kernel of the step touches before the wait.  Launch latency and the ramp-up of the weight
+// another kernel of the step touches before the wait, and what an earlier kernel wrote is read with
+// ordinary loads only (no ld.global.nc, no `const __restrict__` pointer: such a load may be moved
+// above the wait, where the data is not there yet).  Launch latency and the ramp-up of the weight
 // stream thus overlap the previous kernel's tail.  PE_B200_PDL=0 switches the launch attribute off
 // (the two instructions are then no-ops).
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }

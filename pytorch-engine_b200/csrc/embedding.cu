@@ -5,7 +5,7 @@
 namespace pe {
 
 template <typename T>
-__global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int* ids,
                                     float* __restrict__ out, int n_tokens, int hidden, int vocab, int* status) {
   pdl_wait();
   pdl_launch_dependents();

@@ -14,9 +14,9 @@
 namespace pe {
 
 template <typename TDelta, typename TOut>
-__global__ void rmsnorm_kernel(float* __restrict__ residual, const TDelta* __restrict__ delta,
+__global__ void rmsnorm_kernel(float* __restrict__ residual, const TDelta* delta,
                                const float* __restrict__ weight, TOut* __restrict__ out,
-                               const int* __restrict__ rows, int n_rows, int dim, float eps) {
+                               const int* rows, int n_rows, int dim, float eps) {
   extern __shared__ float row_buf[];  // dim floats
   __shared__ float red[32];
   pdl_wait();
@@ -67,9 +67,9 @@ template <> struct Vec4<__nv_bfloat16> {
 };
 
 template <typename TDelta, typename TOut>
-__global__ void rmsnorm_vec4_kernel(float* __restrict__ residual, const TDelta* __restrict__ delta,
+__global__ void rmsnorm_vec4_kernel(float* __restrict__ residual, const TDelta* delta,
                                     const float* __restrict__ weight, TOut* __restrict__ out,
-                                    const int* __restrict__ rows, int n_rows, int dim, float eps) {
+                                    const int* rows, int n_rows, int dim, float eps) {
   extern __shared__ float row_buf[];  // dim floats
   __shared__ float red[32];
   pdl_wait();
@@ -103,7 +103,7 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ residual, const TDelta* 
 // Plain RMSNorm of a tensor in the run dtype (rows of any width), used by parts that normalise
 // something other than the residual stream.
 template <typename T>
-__global__ void rmsnorm_plain_kernel(const T* __restrict__ x, const float* __restrict__ weight, T* __restrict__ out,
+__global__ void rmsnorm_plain_kernel(const T* x, const float* __restrict__ weight, T* __restrict__ out,
                                      int n_rows, int dim, float eps) {
   extern __shared__ float row_buf[];
   __shared__ float red[32];

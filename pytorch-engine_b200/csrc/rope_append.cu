@@ -11,7 +11,7 @@
 namespace pe {
 
 // token_seq[t] = index of the batch entry that token t belongs to; token_pos[t] = its position.
-__global__ void batch_expand_kernel(const int* __restrict__ seq_qstart, const int* __restrict__ seq_past,
+__global__ void batch_expand_kernel(const int* seq_qstart, const int* seq_past,
                                     int n_seqs, int* __restrict__ token_seq, int* __restrict__ token_pos) {
   pdl_wait();
   pdl_launch_dependents();

@@ -7,7 +7,7 @@
 namespace pe {
 
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_rows, int inter,
+__global__ void silu_mul_kernel(const T* gate_up, T* __restrict__ out, int n_rows, int inter,
                                 size_t in_stride) {
   pdl_wait();
   pdl_launch_dependents();
