@@ -34,6 +34,9 @@ __device__ __forceinline__ void report(int* status, int code, int a = 0, int b =
   }
 }
 
+// SMs of a B200.  Used only to size grids and in launch heuristics, never for correctness.
+constexpr int kSMs = 148;
+
 // ---- programmatic dependent launch -------------------------------------------------------------
 // Every kernel of this library is launched so that it may start while its predecessor in the stream
 // is still draining: it does whatever does not depend on earlier kernels (a matrix product starts

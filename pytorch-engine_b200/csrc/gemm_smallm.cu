@@ -201,8 +201,8 @@ static int launch(const Args& a, cudaStream_t stream) {
   // M <= 8 kernels (128 registers) and 12 of the M <= 16 kernels (up to 168 registers) as long as their
   // blocks have at most 4 warps; a block of 8 would be alone on its SM.
   constexpr int kMaxWarps = NT == 1 ? 8 : 4;
-  const long long slots = 148LL * (NT == 1 ? 16 : 12);
-  const long long want_warps = 148LL * 24;
+  const long long slots = (long long)kSMs * (NT == 1 ? 16 : 12);
+  const long long want_warps = (long long)kSMs * 24;
   int warps = 1;
   while (warps < kMaxWarps && (long long)blocks * warps < want_warps && kblocks / (warps * 2) >= 2 * U) warps *= 2;
   // A second wave that fills less than half of the GPU costs more than longer K slices in one wave

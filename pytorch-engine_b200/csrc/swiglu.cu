@@ -29,7 +29,7 @@ extern "C" int pe_silu_mul(int dtype, const void* gate_up, void* out, int n_rows
   const size_t total = (size_t)n_rows * inter;
   const int threads = 256;
   size_t blocks = (total + threads - 1) / threads;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > pe::kSMs * 16) blocks = pe::kSMs * 16;
   if (dtype == PE_F32)
     pe::launch(pe::silu_mul_kernel<float>, (int)blocks, threads, 0, stream, (const float*)gate_up, (float*)out, n_rows, inter, (size_t)2 * inter);
   else if (dtype == PE_BF16)

@@ -17,7 +17,9 @@ class Sampler:
         it in one copy (``Runtime.fetch_tokens``), which also raises if a kernel reported an error."""
         self.device = torch.device(device)
         self.runtime = runtime
-        self._stager = None
+        self._stager = None     # made at the first draw, with the two halves of _meta
+        self._meta = None
+        self._meta_turn = 0
         self._scratch = None
 
     def _scratch_for(self, logits: torch.Tensor, params: SamplingParams) -> Optional[torch.Tensor]:
@@ -38,7 +40,6 @@ class Sampler:
             self._stager = PinnedStager(self.device)
             # two halves used in turn: a launched sampler may still read one while the next is being filled
             self._meta = torch.empty(2, 2 * rt.max_result_rows, dtype=torch.int32, device=self.device)
-            self._meta_turn = 0
         self._meta_turn ^= 1
         meta = self._meta[self._meta_turn, :2 * n]
         self._stager.send(list(requests) + list(steps), meta)
