@@ -23,17 +23,28 @@ class BufferPool:
     def __init__(self, device) -> None:
         self.device = torch.device(device)
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}   # (name, dtype, shape) -> view of the current buffer
 
     def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        shape = tuple(int(s) for s in shape)
+        view = self._views.get((name, dtype, shape))
+        if view is not None:
+            return view
         numel = 1
         for s in shape:
-            numel *= int(s)
+            numel *= s
         key = (name, dtype)
         buf = self._bufs.get(key)
         if buf is None or buf.numel() < numel:
             buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
             self._bufs[key] = buf
-        return buf[:numel].view(*shape)
+            for k in [k for k in self._views if k[0] == name and k[1] == dtype]:
+                del self._views[k]                     # views of the buffer that was replaced
+        if len(self._views) > 4096:                    # steps of ever new sizes: start over
+            self._views.clear()
+        view = buf[:numel].view(*shape)
+        self._views[(name, dtype, shape)] = view
+        return view
 
     def nbytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
