@@ -42,7 +42,7 @@ struct Args {
   const int* page_table; int table_stride; int num_pages;
   const __nv_bfloat16* k_pages; const __nv_bfloat16* v_pages;
   int* status;
-  float* part_acc; float* part_lse; int split_keys, max_splits;
+  float* part_acc; float* part_lse; int split_keys, max_splits, min_range_keys;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -369,12 +369,14 @@ __device__ __forceinline__ void decode_fold_page(uint32_t ks_base, uint32_t vs_b
 
 // ---- decode ------------------------------------------------------------------------------------------
 // Keys per range of a sequence of `len` keys: the fixed split_keys, or (split_keys == 0) the
-// sequence's own length shared out evenly over max_splits ranges, in whole pages.  With even shares
-// a grid sized for the longest possible sequence keeps all its blocks busy on shorter ones.
+// sequence's own length shared out evenly over max_splits ranges, in whole pages, but no fewer than
+// min_range_keys.  With even shares a grid sized for the longest possible sequence keeps all its
+// blocks busy on shorter ones; the floor keeps a short sequence in a grid sized for a much longer
+// one from being cut into ranges of a page or two (its spare blocks return at once).
 __device__ __forceinline__ int range_keys(const Args& a, int len) {
   if (a.split_keys > 0) return a.split_keys;
   const int per = (len + a.max_splits - 1) / a.max_splits;
-  return max(BN, (per + BN - 1) / BN * BN);
+  return max(max(BN, a.min_range_keys), (per + BN - 1) / BN * BN);
 }
 
 // grid: (max_splits, n_kv_heads, n_seqs); block: 128 threads; STAGES pages in flight.
@@ -603,7 +605,8 @@ extern "C" int pe_attention_mma(int decode, const void* q, long long q_ld, void*
                                 int max_q, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
                                 const int* seq_qstart, const int* seq_past, const int* seq_slot, const int* page_table,
                                 int table_stride, int num_pages, const void* k_pages, const void* v_pages,
-                                float* scratch, int split_keys, int max_splits, int* status, cudaStream_t stream) {
+                                float* scratch, int split_keys, int max_splits, int min_range_keys, int* status,
+                                cudaStream_t stream) {
   if (n_seqs <= 0) return PE_OK;
   if (!pe_attention_mma_supported(head_dim, n_heads, n_kv_heads)) return PE_ERR_UNSUPPORTED_SIZE;
   // 16-byte vector loads of q rows
@@ -616,10 +619,11 @@ extern "C" int pe_attention_mma(int decode, const void* q, long long q_ld, void*
   a.seq_qstart = seq_qstart; a.seq_past = seq_past; a.seq_slot = seq_slot;
   a.page_table = page_table; a.table_stride = table_stride; a.num_pages = num_pages;
   a.k_pages = (const __nv_bfloat16*)k_pages; a.v_pages = (const __nv_bfloat16*)v_pages; a.status = status;
-  a.part_acc = nullptr; a.part_lse = nullptr; a.split_keys = 0; a.max_splits = 0;
+  a.part_acc = nullptr; a.part_lse = nullptr; a.split_keys = 0; a.max_splits = 0; a.min_range_keys = 0;
   if (decode) {
     if (!scratch || split_keys < 0 || split_keys % pe::fa::BN || max_splits <= 0) return PE_ERR_BAD_ARGUMENT;
-    a.split_keys = split_keys; a.max_splits = max_splits;
+    if (min_range_keys < 0 || min_range_keys % pe::fa::BN) return PE_ERR_BAD_ARGUMENT;
+    a.split_keys = split_keys; a.max_splits = max_splits; a.min_range_keys = min_range_keys;
     a.part_acc = scratch;
     a.part_lse = scratch + (size_t)n_seqs * n_heads * max_splits * head_dim;
   }

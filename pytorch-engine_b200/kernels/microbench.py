@@ -116,7 +116,8 @@ def prefill_attention(cfg, device, lengths: Sequence[int] = (2048, 4096, 8192, 5
 
 
 def decode_attention(cfg, device, cases: Sequence[Sequence[int]] = ((8, 4090), (1, 4090), (16, 4090), (64, 4090))) -> None:
-    """Split + merge decode attention with ranges of 512 keys, the ranges the engine picks, and other even splits."""
+    """Split + merge decode attention with ranges of 512 keys, the ranges the engine picks (for a cache of
+    this context and of ten times this context), and other even splits."""
     nh, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     flush = _flush_buffer(device)
     for batch, length in cases:
@@ -132,18 +133,23 @@ def decode_attention(cfg, device, cases: Sequence[Sequence[int]] = ((8, 4090), (
         status = torch.zeros(4, dtype=torch.int32, device=device)
         max_kv = -(-length // 64) * 64
 
-        def make(split_keys, max_splits):
+        def make(split_keys, max_splits, least=0):
             out = torch.zeros(batch, nh * d, device=device, dtype=torch.bfloat16)
             scratch = torch.zeros(ops.attention_generic_scratch_floats(batch, nh, d, max_splits), device=device)
             return lambda: ops.attention_mma(True, q, out, batch, 1, nh, nkv, d, 1 / math.sqrt(d), 0, qstart, past, slot,
-                                             table, pages, kp, vp, scratch, split_keys, max_splits, status)
+                                             table, pages, kp, vp, scratch, split_keys, max_splits, status,
+                                             min_range_keys=least)
 
         picked = ops.attention_mma_decode_ranges(torch.device(device), d, batch, nkv, max_kv, 512)
-        configs = [(512, -(-max_kv // 512)), picked] + [(0, n) for n in (2, 4, 8, 16) if batch * nkv * n <= 1200]
+        # the engine's pick for a cache that allows sequences ten times as long: the least range size keeps
+        # this context's ranges as they are, its spare blocks return at once
+        roomy = ops.attention_mma_decode_ranges(torch.device(device), d, batch, nkv, 10 * max_kv, 512)
+        configs = [(512, -(-max_kv // 512)), picked, roomy] + [(0, n) for n in (2, 4, 8, 16) if batch * nkv * n <= 1200]
         t = time_in_turn([make(*c) for c in configs], flush, rounds=12)
         nbytes = 2 * batch * length * nkv * d * 2
         cells = [f"{c}: {us:.1f} us ({nbytes / us / 1e6:.2f} TB/s)" for c, us in zip(configs, t)]
-        print(f"batch {batch} context {length} (split_keys, ranges): " + "  ".join(cells) + f"  [engine picks {picked}]",
+        print(f"batch {batch} context {length} (split_keys, ranges[, least keys]): " + "  ".join(cells) +
+              f"  [engine picks {picked}; {roomy} in a cache for {10 * max_kv} keys]",
               flush=True)
 
 

@@ -154,15 +154,17 @@ def attention_mma(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: int,
                   n_kv_heads: int, head_dim: int, scale: float, window: int, seq_qstart: torch.Tensor,
                   seq_past: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int,
                   k_pages: torch.Tensor, v_pages: torch.Tensor, scratch: Optional[torch.Tensor], split_keys: int,
-                  max_splits: int, status: torch.Tensor) -> None:
-    """Same contract as ``attention_generic``, bfloat16 only, head sizes 64 and 128, groups up to 16."""
+                  max_splits: int, status: torch.Tensor, min_range_keys: int = 0) -> None:
+    """Same contract as ``attention_generic``, bfloat16 only, head sizes 64 and 128, groups up to 16.
+    With ``split_keys`` 0 a sequence's keys are shared out evenly over ``max_splits`` ranges of whole pages,
+    each of at least ``min_range_keys`` keys."""
     _need(q.stride(-1) == 1 and out.stride(-1) == 1, "attention: rows must be contiguous")
     _need(q.dtype == out.dtype == k_pages.dtype == torch.bfloat16, "attention_mma: bfloat16 tensors only")
     check(library().pe_attention_mma(
         1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), n_seqs, max_q, n_heads, n_kv_heads,
         head_dim, float(scale), int(window), _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot), _ptr(page_table),
         page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages), _ptr(scratch), split_keys, max_splits,
-        _ptr(status), _stream()), "attention_mma")
+        int(min_range_keys), _ptr(status), _stream()), "attention_mma")
     _count(2 if decode else 1)
 
 
@@ -246,20 +248,22 @@ def gemm_umma2(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, status:
 
 
 def decode_ranges(slots: int, pairs: int, max_kv_len: int, split_keys: int) -> tuple:
-    """(split_keys, max_splits) for a decode attention whose SMs hold ``slots`` blocks at a time and that
-    has ``pairs`` (sequence, kv head) pairs; split_keys 0 means that each sequence's keys are shared
-    out evenly over max_splits ranges (in whole pages).  When one wave of blocks can hold at least two
-    ranges per pair, that many ranges are used, but not more than ranges of ``split_keys`` keys would
-    give (measured: the blocks of a second, partly filled wave cost more than longer ranges do, and
-    more, shorter ranges only add merge work).  With more pairs than that there are several waves
-    anyway, and ranges of about four times ``split_keys`` keys were measured best (batch 64 at 4,096
-    keys: 169 us with two ranges, 179 us with eight)."""
+    """(split_keys, max_splits, min_range_keys) for a decode attention whose SMs hold ``slots`` blocks at a
+    time and that has ``pairs`` (sequence, kv head) pairs; split_keys 0 means that each sequence's keys
+    are shared out evenly over max_splits ranges (in whole pages, of at least min_range_keys keys).
+    When one wave of blocks can hold at least two ranges per pair, that many ranges are used, but not
+    more than ranges of ``split_keys`` keys would give (measured: the blocks of a second, partly filled
+    wave cost more than longer ranges do, and more, shorter ranges only add merge work).  With more
+    pairs than that there are several waves anyway, and ranges of about four times ``split_keys`` keys
+    were measured best (batch 64 at 4,096 keys: 169 us with two ranges, 179 us with eight).  The same
+    two sizes are the least a range may have: ``max_kv_len`` is the longest sequence the cache allows,
+    and a sequence far shorter than that is not to be cut into as many ranges."""
     pairs = max(1, pairs)
     fixed = max(1, -(-max_kv_len // split_keys))
     per_pair = slots // pairs
     if per_pair < 2:
-        return 0, max(1, min(fixed, -(-max_kv_len // (4 * split_keys))))
-    return 0, min(per_pair, fixed)
+        return 0, max(1, min(fixed, -(-max_kv_len // (4 * split_keys)))), 4 * split_keys
+    return 0, min(per_pair, fixed), split_keys
 
 
 def attention_mma_decode_ranges(device: torch.device, head_dim: int, n_seqs: int, n_kv_heads: int, max_kv_len: int,

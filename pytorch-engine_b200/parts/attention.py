@@ -117,10 +117,12 @@ class GQAttention:
         scratch = None
         max_splits = 0
         split_keys = SPLIT_KEYS
+        extra = {}
         if ctx.decode:
             if self.use_mma:
-                split_keys, max_splits = ops.attention_mma_decode_ranges(
+                split_keys, max_splits, floor = ops.attention_mma_decode_ranges(
                     q.device, self.head_dim, ctx.n_seqs, self.n_kv_heads, ctx.max_kv_len, SPLIT_KEYS)
+                extra["min_range_keys"] = floor
             else:
                 max_splits = ctx.max_splits(split_keys)
             scratch = ctx.buffer(
@@ -131,4 +133,4 @@ class GQAttention:
         kernel(
             ctx.decode, q, out, ctx.n_seqs, ctx.max_q, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
             self.window, ctx.seq_qstart, ctx.seq_past, ctx.seq_slot, view.page_table, view.num_pages, view.k_pages,
-            view.v_pages, scratch, split_keys, max_splits, self.runtime.status)
+            view.v_pages, scratch, split_keys, max_splits, self.runtime.status, **extra)

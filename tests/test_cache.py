@@ -176,14 +176,15 @@ def test_a_step_that_cannot_get_all_its_pages_takes_none(pe):
 def test_decode_attention_ranges(pe):
     """How many ranges a sequence's keys are shared out over (the decision only; no device)."""
     f = pe.kernels.ops.decode_ranges
-    assert f(296, 8 * 8, 4096, 512) == (0, 4)        # batch 8, 8 kv heads: four ranges make one wave of 256 blocks
-    assert f(296, 1 * 8, 4096, 512) == (0, 8)        # batch 1: no more ranges than 512 keys each
-    assert f(296, 1 * 8, 16384, 512) == (0, 32)
-    assert f(296, 16 * 8, 4096, 512) == (0, 2)
-    assert f(296, 64 * 8, 4096, 512) == (0, 2)       # several waves anyway: ranges of about 2,048 keys
-    assert f(296, 64 * 8, 32768, 512) == (0, 16)
-    assert f(296, 64 * 8, 100, 512) == (0, 1)
-    assert f(296, 3, 40, 512) == (0, 1)              # a short context is one range
+    assert f(296, 8 * 8, 4096, 512) == (0, 4, 512)   # batch 8, 8 kv heads: four ranges make one wave of 256 blocks
+    assert f(296, 1 * 8, 4096, 512) == (0, 8, 512)   # batch 1: no more ranges than 512 keys each
+    assert f(296, 1 * 8, 16384, 512) == (0, 32, 512)
+    assert f(296, 1 * 8, 40960, 512) == (0, 37, 512)  # a roomy cache: 37 ranges in the grid, of at least 512 keys each
+    assert f(296, 16 * 8, 4096, 512) == (0, 2, 512)
+    assert f(296, 64 * 8, 4096, 512) == (0, 2, 2048)  # several waves anyway: ranges of about 2,048 keys
+    assert f(296, 64 * 8, 32768, 512) == (0, 16, 2048)
+    assert f(296, 64 * 8, 100, 512) == (0, 1, 2048)
+    assert f(296, 3, 40, 512) == (0, 1, 512)          # a short context is one range
     for slots, pairs, kv in [(296, 7, 5000), (592, 100, 70000), (10, 1000, 64)]:
-        sk, n = f(slots, pairs, kv, 512)
-        assert sk == 0 and 1 <= n <= max(1, -(-kv // 512))
+        sk, n, least = f(slots, pairs, kv, 512)
+        assert sk == 0 and 1 <= n <= max(1, -(-kv // 512)) and least in (512, 2048)

@@ -461,8 +461,9 @@ def test_attention_umma_prefill_rescales_when_the_maximum_grows(ops):
 
 @pytest.mark.parametrize("nh,nkv,d", MMA_SHAPES)
 @pytest.mark.parametrize("window", [0, 300])
-@pytest.mark.parametrize("split_keys,max_splits", [(256, 5), (0, 5), (0, 1), (0, 23)])   # 0: even shares of each length
-def test_attention_mma_decode(ops, nh, nkv, d, window, split_keys, max_splits):
+# split_keys 0: even shares of each length, of at least `least` keys (spare ranges of the grid do nothing)
+@pytest.mark.parametrize("split_keys,max_splits,least", [(256, 5, 0), (0, 5, 0), (0, 1, 0), (0, 23, 0), (0, 23, 128), (0, 9, 512)])
+def test_attention_mma_decode(ops, nh, nkv, d, window, split_keys, max_splits, least):
     torch.manual_seed(16)
     dtype = torch.bfloat16
     lens = [1, 700, 256, 257, 33, 64, 65, 513]
@@ -478,7 +479,7 @@ def test_attention_mma_decode(ops, nh, nkv, d, window, split_keys, max_splits):
     scratch = torch.full((ops.attention_generic_scratch_floats(B, nh, d, max_splits),), float("nan"), device=DEV)
     st = _status()
     ops.attention_mma(True, q_all, out, B, 1, nh, nkv, d, scale, window, qstart, past_t, ps.seq_slot, ps.table,
-                      ps.num_pages, ps.k_pages, ps.v_pages, scratch, split_keys, max_splits, st)
+                      ps.num_pages, ps.k_pages, ps.v_pages, scratch, split_keys, max_splits, st, min_range_keys=least)
     assert st.tolist()[0] == 0
     qs = [q_all[b: b + 1, : nh * d].cpu().view(1, nh, d) for b in range(B)]
     want = _plain_attention(ps, qs, pasts, nh, scale, window or None)
