@@ -75,13 +75,16 @@ class _LoopBackend:
 class Engine:
     def __init__(self, model_path: Optional[str] = None, *, dtype: Union[str, torch.dtype] = "bfloat16",
                  max_context_len: Optional[int] = None, max_cache_tokens: Optional[int] = None, max_batch: int = 64,
-                 max_slots: Optional[int] = None, enable_cuda_graph: bool = True, device: str = "cuda:0",
+                 max_slots: Optional[int] = None, max_step_tokens: Optional[int] = 65536,
+                 enable_cuda_graph: bool = True, device: str = "cuda:0",
                  config: Optional[ModelConfig] = None, weights: Optional[Dict[str, torch.Tensor]] = None,
                  verbose: bool = False) -> None:
         """``model_path``: a folder with config.json and model.safetensors.  ``max_context_len``: the
         longest sequence (default: the configuration's ``max_position_embeddings``).
         ``max_cache_tokens``: how many tokens all live sequences may hold together, each rounded up
-        to 64 (default: ``max_batch`` sequences of full length, capped by free memory)."""
+        to 64 (default: ``max_batch`` sequences of full length, capped by free memory).
+        ``max_step_tokens``: the most prompt tokens that generation feeds in one step (None: no limit); the
+        buffers of a step, beside the cache, grow with its tokens (about 100 KB per token at the 8B shape)."""
         t0 = time.perf_counter()
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device is visible: this engine runs on a B200 (sm_100a) only and has no CPU path")
@@ -117,7 +120,8 @@ class Engine:
         self.runner = ModelRunner(self.model, self.cache, cuda_graphs=enable_cuda_graph)
         self.sampler = Sampler(self.device, self.runtime)
         self.loop = GenerationLoop(_LoopBackend(self), max_context=self.max_context_len, max_batch=self.max_batch,
-                                   eos_token_ids=config.stop_token_ids, bos_token_id=config.bos_token)
+                                   eos_token_ids=config.stop_token_ids, bos_token_id=config.bos_token,
+                                   max_step_tokens=max_step_tokens)
         self.load_time_s = time.perf_counter() - t0
         if verbose:
             rep = self.memory_report()

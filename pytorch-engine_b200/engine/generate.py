@@ -74,10 +74,16 @@ class _Live:
 
 class GenerationLoop:
     def __init__(self, backend, *, max_context: int, max_batch: int, eos_token_ids: Sequence[int] = (),
-                 bos_token_id: int = 0) -> None:
+                 bos_token_id: int = 0, max_step_tokens: Optional[int] = None) -> None:
+        """``max_step_tokens``: the most prompt tokens one step brings (None: no limit).  A batch whose
+        prompts hold more goes through several steps, a prompt longer than that in pieces: what a step
+        needs beside the cache grows with its tokens."""
         self.backend = backend
         self.max_context = int(max_context)
         self.max_batch = int(max_batch)
+        self.max_step_tokens = int(max_step_tokens) if max_step_tokens else None
+        if self.max_step_tokens is not None and self.max_step_tokens < 1:
+            raise ValueError("max_step_tokens must be positive")
         self.eos_token_ids = tuple(eos_token_ids)
         self.bos_token_id = int(bos_token_id)
 
@@ -116,6 +122,26 @@ class GenerationLoop:
             batches.append(cur)
         return batches
 
+    def plan_prefill(self, lengths: Sequence[int]) -> List[List[Tuple[int, int, int]]]:
+        """The steps that bring a batch's prompts in: each a list of (sequence, first token, end) in
+        the batch's order, together at most ``max_step_tokens`` tokens.  One step if that fits."""
+        budget = self.max_step_tokens
+        if budget is None or sum(lengths) <= budget:
+            return [[(i, 0, n) for i, n in enumerate(lengths)]]
+        steps: List[List[Tuple[int, int, int]]] = [[]]
+        used = 0
+        for i, n in enumerate(lengths):
+            at = 0
+            while at < n:
+                if used == budget:
+                    steps.append([])
+                    used = 0
+                take = min(n - at, budget - used)
+                steps[-1].append((i, at, at + take))
+                at += take
+                used += take
+        return steps
+
     # ---- the loop ----------------------------------------------------------------------------
     def stream(self, prompts: Sequence[Sequence[int]], params: Optional[SamplingParams] = None) -> Iterator[StreamChunk]:
         params = params or SamplingParams()
@@ -135,8 +161,15 @@ class GenerationLoop:
                 live.append(_Live(request=i, slot=be.alloc_slot(), prompt=prompts[i],
                                   max_new=self.new_token_limit(len(prompts[i]), params.max_tokens)))
             t0 = time.perf_counter()
-            logits = be.step([StepEntry(s.slot, s.prompt, (len(s.prompt) - 1,)) for s in live])
-            tokens = self._draw(logits, live, params, seed)
+            tokens = [0] * len(live)
+            for pieces in self.plan_prefill([len(s.prompt) for s in live]):
+                # a sequence's first token is drawn in the step that brings the end of its prompt
+                ends = [i for i, _, end in pieces if end == len(live[i].prompt)]
+                logits = be.step([StepEntry(live[i].slot, live[i].prompt[a:b], (b - a - 1,) if b == len(live[i].prompt) else ())
+                                  for i, a, b in pieces])
+                if ends:
+                    for i, tok in zip(ends, self._draw(logits, [live[i] for i in ends], params, seed)):
+                        tokens[i] = tok
             prefill_s = time.perf_counter() - t0
             t_decode = time.perf_counter()
 

@@ -33,7 +33,7 @@ class FakeBackend:
         assert len({e.slot for e in entries}) == len(entries)
         assert all(e.slot in self.held for e in entries)
         self.steps.append([(e.slot, list(e.tokens), tuple(e.want)) for e in entries])
-        return len(entries)
+        return sum(len(e.want) for e in entries)     # stands for the logits: one row per wanted place
 
     def sample(self, logits, params, seed, requests, steps, recent=None):
         assert logits == len(requests)
@@ -203,3 +203,26 @@ def test_one_step_ahead_stream_order_and_stats(pe):
     assert [(c.request, c.token_id, c.finish_reason) for c in chunks] == [
         (0, 10, None), (1, 20, None), (0, 11, None), (1, 99, "stop"), (0, 12, None), (0, 13, "length")]
     assert chunks[-1].stats.token_ids == [10, 11, 12, 13]
+
+
+def test_prompts_beyond_the_step_limit_come_in_several_steps(pe):
+    lp = _loop(pe, FakeBackend({}), max_step_tokens=5)
+    assert lp.plan_prefill([2, 3]) == [[(0, 0, 2), (1, 0, 3)]]                       # fits: one step
+    assert lp.plan_prefill([4, 3, 7]) == [[(0, 0, 4), (1, 0, 1)], [(1, 1, 3), (2, 0, 3)], [(2, 3, 7)]]
+    assert _loop(pe, FakeBackend({})).plan_prefill([100, 200]) == [[(0, 0, 100), (1, 0, 200)]]   # no limit
+    scripts = {0: [10, 11], 1: [20, 99], 2: [30, 31]}
+    be = FakeBackend(scripts)
+    prompts = [[1, 2, 3, 4], [5, 6, 7], [8, 9, 10, 11, 12, 13, 14]]
+    res = _loop(pe, be, max_step_tokens=5).generate(prompts, pe.SamplingParams(max_tokens=2, temperature=0.0))
+    assert [r.token_ids for r in res] == [[10, 11], [20], [30, 31]]
+    # three steps bring the prompts; logits are wanted only where a prompt ends
+    assert [[(t, w) for _, t, w in st] for st in be.steps[:3]] == [
+        [([1, 2, 3, 4], (3,)), ([5], ())], [([6, 7], (1,)), ([8, 9, 10], ())], [([11, 12, 13, 14], (3,))]]
+    # each sequence's first token is drawn when its prompt is through, keyed by its own request and step
+    assert be.sample_calls[:3] == [([0], [0]), ([1], [0]), ([2], [0])]
+    assert [[t for _, t, _ in st] for st in be.steps[3:]] == [[[10], [20], [30]]]
+    assert not be.held
+    # the same requests without a limit give the same tokens
+    be2 = FakeBackend(scripts)
+    res2 = _loop(pe, be2).generate(prompts, pe.SamplingParams(max_tokens=2, temperature=0.0))
+    assert [r.token_ids for r in res2] == [r.token_ids for r in res]

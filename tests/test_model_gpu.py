@@ -322,6 +322,20 @@ def test_streaming_leaves_the_callers_grad_mode_alone_and_frees_slots_when_aband
         [r.token_ids for r in whole]
 
 
+def test_prompts_fed_in_several_steps_give_the_same_tokens(pe, engines, oracles):
+    """A step limit of 37 tokens cuts these prompts into pieces, one of them in the middle of a page."""
+    cfg, w = oracles["B"]
+    prompts = [_tokens(cfg["vocab_size"], n, 200 + n) for n in (70, 3, 130, 36)]
+    params = pe.SamplingParams.greedy_params(max_tokens=6)
+    whole = engines("B", "float32").generate(prompts, params)
+    cut = engines("B", "float32", max_step_tokens=37)
+    pieces = cut.generate(prompts, params)
+    assert [r.token_ids for r in pieces] == [r.token_ids for r in whole]
+    assert pieces[3].token_ids == plain.generate_greedy(cfg, w, prompts[3], 6)
+    assert not cut.cache.live_slots
+    cut.cache.check()
+
+
 def test_stop_token_and_context_limit(pe, engines, oracles):
     cfg, w = oracles["A"]
     eng = engines("A", "float32")
