@@ -29,6 +29,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--dtype", choices=["bf16", "bfloat16", "fp32", "float32"], default="bf16")
     p.add_argument("--ctx", type=int, default=None, help="max context window (default: the model's)")
     p.add_argument("--max-batch", type=int, default=64, help="most sequences decoded together")
+    p.add_argument("--max-step-tokens", type=int, default=65536, help="most prompt tokens fed in one step (0: no limit)")
     p.add_argument("--no-cuda-graph", action="store_true", help="disable CUDA graph replay of decode steps")
     pr = p.add_argument_group("prompts (token ids)")
     pr.add_argument("--prompt-ids", action="append", default=[], metavar="1,2,3", help="a prompt as token ids; repeatable")
@@ -83,6 +84,7 @@ def main(argv=None) -> int:
         print("no prompt given (--prompt-ids, --prompt-file or --random-prompts)", file=sys.stderr)
         return 2
     kw = dict(dtype=args.dtype, max_context_len=args.ctx, max_batch=args.max_batch,
+              max_step_tokens=args.max_step_tokens or None,
               enable_cuda_graph=not args.no_cuda_graph, verbose=not args.json)
     engine = Engine(args.model, **kw) if args.model else Engine.from_random(cfg, args.seed, **kw)
     params = SamplingParams(max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k,
