@@ -102,6 +102,13 @@ class PagedCache:
             g.entries.append(entry_id)
         for g in self.groups:
             self._allocate(g)
+        # New page numbers reach the device through pinned memory and an asynchronous copy on the current
+        # stream: a copy from pageable memory would make the host wait for every step still queued, once
+        # per page a sequence begins.  The ring is deep enough for two steps of a full batch.
+        self._stager = None
+        if self.device.type == "cuda":
+            from ..staging import PinnedStager
+            self._stager = PinnedStager(self.device, capacity=max(64, self.table_width), depth=256)
 
     # ---- storage -------------------------------------------------------------------------
     def _allocate(self, g: CacheGroup) -> None:
@@ -196,7 +203,10 @@ class PagedCache:
                 start = len(have)
                 new_pages = g.pool.take_many(need - start)
                 have.extend(new_pages)
-                g.page_table[slot, start:need] = torch.tensor(new_pages, dtype=torch.int32)
+                if self._stager is not None:
+                    self._stager.send(new_pages, g.page_table[slot, start:need])
+                else:
+                    g.page_table[slot, start:need] = torch.tensor(new_pages, dtype=torch.int32)
 
     def release_reserved(self, slot: int) -> None:
         """Give back the pages that ``reserve`` took beyond the sequence's committed length (a step
