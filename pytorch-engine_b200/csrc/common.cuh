@@ -63,8 +63,8 @@ inline bool pdl_enabled() {
 }
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                          Args... args) {
+inline cudaError_t launch_as(bool early_start, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -74,8 +74,23 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = (early_start && pdl_enabled()) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// The usual launch: the kernel may start while its predecessor drains.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args... args) {
+  return launch_as(true, kernel, grid, block, smem, stream, args...);
+}
+
+// A launch that starts only when its predecessor has completed (the two instructions in the kernel are
+// then no-ops for it; its own successor may still start early).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args... args) {
+  return launch_as(false, kernel, grid, block, smem, stream, args...);
 }
 
 // ---- element conversion ----------------------------------------------------------------------
