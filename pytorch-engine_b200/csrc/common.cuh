@@ -49,7 +49,8 @@ constexpr int kSMs = 148;
 // ordinary loads only (no ld.global.nc, no `const __restrict__` pointer: such a load may be moved
 // above the wait, where the data is not there yet).  Launch latency and the ramp-up of the weight
 // stream thus overlap the previous kernel's tail.  PE_B200_PDL=0 switches the launch attribute off
-// (the two instructions are then no-ops).
+// (the two instructions are then no-ops).  One kernel is launched without it, because that was measured
+// faster: the merge of the decode attention's ranges (attention_mma.cu).
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
