@@ -113,7 +113,7 @@ __device__ __forceinline__ void fold_tile(const float* qs /*[kGT][d]*/, const fl
 template <typename T, int DPL>
 __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a) {
   extern __shared__ float smem[];
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   constexpr int W = 8;
   const int d = a.head_dim;
@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a) {
 template <typename T, int DPL, int NW>
 __global__ void __launch_bounds__(NW * 32) attn_decode_split_kernel(AttnArgs a) {
   extern __shared__ float smem[];
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int d = a.head_dim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_split_kernel(AttnArgs a) 
 // grid: (n_heads, n_seqs); merges the ranges that the split kernel wrote for this sequence.
 template <typename T>
 __global__ void attn_decode_combine_kernel(AttnArgs a) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int b = blockIdx.y, h = blockIdx.x;
   const int d = a.head_dim;

@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
                                                       const __grid_constant__ CUtensorMap vmap) {
   extern __shared__ char smem_raw[];
   __shared__ uint64_t bars[2];
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   char* smem = align_1024(smem_raw);
   constexpr int STAGE = 2 * BN * HD * 2;      // K and V tile
@@ -418,7 +418,7 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
       if (s < n_tiles && k_begin + s * BN != last_page_k0)
         issue_page<HD>(a, &kmap, &vmap, slot, kvh, k_begin + s * BN, smem + s * STAGE, &bars[s]);
   }
-  pdl_wait();
+  pdl_wait_block();
   if (tid == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s)
@@ -499,7 +499,7 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
 // grid: (n_heads, n_seqs): merge the ranges of one (sequence, head) (pygguf_engine/kv_cache.py:273-282).
 template <int HD>
 __global__ void decode_merge_kernel(Args a) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int b = blockIdx.y, h = blockIdx.x;
   const int tq = a.seq_qstart[b];

@@ -141,7 +141,7 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
   // All shared memory is dynamic and starts on a 1,024-byte boundary (there are no static shared
   // variables in front of it), so that two blocks fit on an SM: tiles first, barriers behind them.
   extern __shared__ __align__(1024) char smem[];
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   char* q_s = smem;                       // [2 halves][128 rows][128 B]
   char* k_s = q_s + kQBytes;              // kKStages K pages

@@ -7,7 +7,7 @@ namespace pe {
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* ids,
                                     float* __restrict__ out, int n_tokens, int hidden, int vocab, int* status) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int row = blockIdx.x;
   if (row >= n_tokens) return;

@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(WARPS * 32, NT == 1 ? 16 / WARPS : 1) gemm_sma
   // slower: 4.37 and 4.67 ms against 4.34 ms for a decode step of 8 sequences.)
   Batch b0, b1;
   load_w(b0, kb_lo);
-  pdl_wait();
+  pdl_wait_block();
   load_x(b0, kb_lo);
   for (int kb = kb_lo; kb < kb_hi; kb += 2 * U) {
     load(b1, kb + U);

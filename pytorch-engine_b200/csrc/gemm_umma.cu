@@ -124,7 +124,7 @@ gemm_umma_kernel(Params p, const __grid_constant__ CUtensorMap amap, const __gri
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = tmem_holder;
-  pdl_wait();  // set-up (barriers, tensor memory) is done; now the inputs must be complete
+  pdl_wait_block();  // set-up (barriers, tensor memory) is done; now the inputs must be complete
   pdl_launch_dependents();
 
   if (warp == 0) {

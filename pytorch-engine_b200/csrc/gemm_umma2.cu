@@ -186,7 +186,7 @@ gemm_umma2_kernel(Params p, const __grid_constant__ CUtensorMap amap, const __gr
   cluster_sync();   // the peer's barriers exist before anything is sent to them
   fence_after_sync();
   const uint32_t tmem_base = tmem_holder;
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
 
   if (warp == 0) {

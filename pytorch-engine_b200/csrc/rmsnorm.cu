@@ -19,7 +19,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ residual, const TDelta* delta
                                const int* rows, int n_rows, int dim, float eps) {
   extern __shared__ float row_buf[];  // dim floats
   __shared__ float red[32];
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int r = blockIdx.x;
   if (r >= n_rows) return;
@@ -72,7 +72,7 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ residual, const TDelta* 
                                     const int* rows, int n_rows, int dim, float eps) {
   extern __shared__ float row_buf[];  // dim floats
   __shared__ float red[32];
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int r = blockIdx.x;
   if (r >= n_rows) return;
@@ -107,7 +107,7 @@ __global__ void rmsnorm_plain_kernel(const T* x, const float* __restrict__ weigh
                                      int n_rows, int dim, float eps) {
   extern __shared__ float row_buf[];
   __shared__ float red[32];
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int r = blockIdx.x;
   if (r >= n_rows) return;

@@ -13,7 +13,7 @@ namespace pe {
 // token_seq[t] = index of the batch entry that token t belongs to; token_pos[t] = its position.
 __global__ void batch_expand_kernel(const int* seq_qstart, const int* seq_past,
                                     int n_seqs, int* __restrict__ token_seq, int* __restrict__ token_pos) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int b = blockIdx.x;
   if (b >= n_seqs) return;
@@ -61,7 +61,7 @@ template <> __device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16*
 // aligned to two elements); otherwise one feature at a time.
 template <typename T, bool PAIRS>
 __global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -210,7 +210,7 @@ __global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
 // walks `tokens_per_block` tokens so that the per-token index loads overlap.
 __global__ void __launch_bounds__(256) qk_norm_rope_append_vec8_kernel(RopeAppendArgs a, int lanes_per_head,
                                                                         int tokens_per_block) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   typedef __nv_bfloat16 T;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -174,7 +174,7 @@ __global__ void __launch_bounds__(kChunkThreads) sample_chunks_kernel(SampleArgs
   __shared__ int red_i[33 * 16];
   __shared__ ArgBest red_b[32];
   __shared__ int scan[kChunkThreads];
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int row = blockIdx.y, chunk = blockIdx.x, tid = threadIdx.x;
   const int lo = chunk * kChunk, n = min(kChunk, a.vocab - lo);
@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleArgs a) {
   __shared__ int scan[kSampleThreads];
   __shared__ float l_val[kMaxCandidates];
   __shared__ int l_idx[kMaxCandidates];
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
@@ -399,7 +399,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleArgs a) {
 // logits[row, id] for the unique ids among recent[row, 0..count): negative -> * penalty, else / penalty.
 __global__ void repetition_penalty_kernel(float* logits, long long ld, int vocab, const int* recent, int recent_stride,
                                           const int* recent_count, float penalty) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const int row = blockIdx.x;
   const int n = min(recent_count[row], recent_stride);

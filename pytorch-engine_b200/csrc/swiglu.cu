@@ -9,7 +9,7 @@ namespace pe {
 template <typename T>
 __global__ void silu_mul_kernel(const T* gate_up, T* __restrict__ out, int n_rows, int inter,
                                 size_t in_stride) {
-  pdl_wait();
+  pdl_wait_block();
   pdl_launch_dependents();
   const size_t total = (size_t)n_rows * inter;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
