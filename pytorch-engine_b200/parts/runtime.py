@@ -52,11 +52,11 @@ class PendingTokens:
 
 def large_gemm_fill(rows: int, cols: int, sms: int) -> float:
     """Share of busy tile slots when ``rows x cols`` outputs are cut into 256 x 256 tiles and run in
-    rounds of one tile per pair of SMs: 96 tiles on 74 pairs need two rounds and fill 0.65 of them."""
+    waves of one tile per pair of SMs: 96 tiles on 74 pairs need two waves and fill 0.65 of them."""
     tiles = -(-rows // 256) * -(-cols // 256)
     pairs = max(1, sms // 2)
-    rounds = -(-tiles // pairs)
-    return tiles / (rounds * pairs)
+    waves = -(-tiles // pairs)
+    return tiles / (waves * pairs)
 
 
 class Runtime:
@@ -83,7 +83,7 @@ class Runtime:
         # refuses, the library product stands (measured: with fewer rows too few tiles exist to fill the SMs)
         self.own_large_gemm = True
         self.large_gemm_rows = 1024
-        self.large_gemm_min_fill = 0.8   # least share of the rounds of tiles that does work (see takes_large_gemm)
+        self.large_gemm_min_fill = 0.8   # least share of the waves of tiles that does work (see takes_large_gemm)
         self.pair_gemm = True       # large products on tcgen05 cta_group::2
 
     # ---- weights -------------------------------------------------------------------------
@@ -119,7 +119,7 @@ class Runtime:
         if not (self.own_large_gemm and x.dim() == 2 and x.shape[0] >= rows
                 and ops.gemm_umma_supported(x, weight, pair_offset)):
             return False
-        # A plain product whose 256 x 256 tiles leave the last round of SM pairs mostly idle goes to the
+        # A plain product whose 256 x 256 tiles leave the last wave of SM pairs mostly idle goes to the
         # library, which has smaller tiles to choose from (8B shape, 1,536 rows, down projection: 96 tiles
         # on 74 pairs took 133 us against 103 us).
         return bool(pair_offset) or large_gemm_fill(x.shape[0], weight.shape[0], ops.sm_count(x.device)) >= self.large_gemm_min_fill

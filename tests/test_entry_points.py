@@ -109,10 +109,10 @@ def test_default_cache_size_is_capped_by_free_memory(pe):
     assert f(2, 64, reqs, torch.float32, "cpu", free_bytes=10) == 64
 
 
-def test_large_products_that_fill_their_rounds_badly_go_to_the_library(pe):
+def test_large_products_that_fill_their_waves_badly_go_to_the_library(pe):
     import importlib
     fill = importlib.import_module("pytorch-engine_b200.parts.runtime").large_gemm_fill
-    assert fill(256, 256 * 74, 148) == 1.0                      # one full round
-    assert abs(fill(1536, 4096, 148) - 96 / 148) < 1e-9         # 96 tiles need two rounds of 74
+    assert fill(256, 256 * 74, 148) == 1.0                      # one full wave
+    assert abs(fill(1536, 4096, 148) - 96 / 148) < 1e-9         # 96 tiles need two waves of 74
     assert fill(2048, 6144, 148) > 0.8 > fill(1024, 6144, 148)
     assert fill(1, 1, 2) == 1.0
