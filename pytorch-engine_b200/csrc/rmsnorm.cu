@@ -67,11 +67,16 @@ template <> struct Vec4<__nv_bfloat16> {
 };
 
 template <typename TDelta, typename TOut>
-__global__ void rmsnorm_vec4_kernel(float* __restrict__ residual, const TDelta* delta,
-                                    const float* __restrict__ weight, TOut* __restrict__ out,
-                                    const int* rows, int n_rows, int dim, float eps) {
+__global__ void __launch_bounds__(1024) rmsnorm_vec4_kernel(float* __restrict__ residual, const TDelta* delta,
+                                                             const float* __restrict__ weight, TOut* __restrict__ out,
+                                                             const int* rows, int n_rows, int dim, float eps) {
   extern __shared__ float row_buf[];  // dim floats
   __shared__ float red[32];
+  // The norm's weight does not depend on the kernels before this one: the part of it that this thread
+  // needs first is on its way before the wait (a decode step waits for this kernel's latency 73 times).
+  const int c0 = threadIdx.x * 4;
+  float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c0 < dim) w0 = Vec4<float>::load(weight + c0);
   pdl_wait_block();
   pdl_launch_dependents();
   const int r = blockIdx.x;
@@ -81,7 +86,7 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ residual, const TDelta* 
   const TDelta* d_row = delta ? delta + src * dim : nullptr;
   const bool write_back = (d_row != nullptr) && (rows == nullptr);
   float ss = 0.f;
-  for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) {
+  for (int c = c0; c < dim; c += blockDim.x * 4) {
     float4 h = Vec4<float>::load(res_row + c);
     if (d_row) {
       const float4 d = Vec4<TDelta>::load(d_row + c);
@@ -93,9 +98,9 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ residual, const TDelta* 
   }
   const float inv = rsqrtf(block_sum(ss, red) / (float)dim + eps);
   TOut* o_row = out + (size_t)r * dim;
-  for (int c = threadIdx.x * 4; c < dim; c += blockDim.x * 4) {
+  for (int c = c0; c < dim; c += blockDim.x * 4) {
     const float4 h = *reinterpret_cast<const float4*>(row_buf + c);
-    const float4 w = Vec4<float>::load(weight + c);
+    const float4 w = c == c0 ? w0 : Vec4<float>::load(weight + c);
     Vec4<TOut>::store(o_row + c, make_float4(h.x * inv * w.x, h.y * inv * w.y, h.z * inv * w.z, h.w * inv * w.w));
   }
 }
@@ -139,10 +144,14 @@ extern "C" int pe_rmsnorm_residual(int dtype, float* residual, const void* delta
   if (dim <= 0) return PE_ERR_BAD_ARGUMENT;
   const size_t smem = (size_t)dim * sizeof(float);
   if (smem > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;  // rows wider than 51,200 features
-  const int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
+  int threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
   int e;
   const bool vec = (dim % 4 == 0) && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
                    ((uintptr_t)out % 16 == 0) && ((uintptr_t)delta % 16 == 0);
+  // A handful of rows (a decode step): what counts is the kernel's latency, and a thread that has a
+  // second 16-byte piece to fetch waits for memory a second time (8B shape, batch 8: 3.97 ms a step with
+  // 512 threads a row, 3.95 with 1,024, 4.08 with 256, 5.18 with 128).
+  if (vec && n_rows <= 64 && dim > 2048) threads = 1024;
   if (dtype == PE_F32) {
     auto k = vec ? pe::rmsnorm_vec4_kernel<float, float> : pe::rmsnorm_kernel<float, float>;
     if ((e = pe::set_smem(k, smem))) return e;
