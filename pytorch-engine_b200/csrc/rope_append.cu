@@ -61,50 +61,78 @@ template <> __device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16*
 // aligned to two elements); otherwise one feature at a time.
 template <typename T, bool PAIRS>
 __global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
-  pdl_wait_block();
-  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y * (blockDim.x >> 5) + warp;
   const int total_heads = a.n_heads + 2 * a.n_kv_heads;
-  if (t >= a.n_tokens || head >= total_heads) return;
+  const bool valid = t < a.n_tokens && head < total_heads;
   const int d = a.head_dim;
-  T* row = (T*)a.qkv + (size_t)t * a.ld + (size_t)head * d;
   const bool is_q = head < a.n_heads;
   const bool is_k = !is_q && head < a.n_heads + a.n_kv_heads;
   const int kv_head = is_q ? -1 : (is_k ? head - a.n_heads : head - a.n_heads - a.n_kv_heads);
-  const int pos = a.token_pos[t];
+  // Before the wait: what does not come from the kernel before this one.  The step's batch description
+  // and the page table were complete before that kernel started, the angle tables and norm weights never
+  // change; only the q|k|v rows have to be waited for.  In a decode step this kernel's latency is on the
+  // critical path, and the chain token -> sequence -> slot -> page is three trips to memory.
+  const bool to_cache = valid && !is_q && a.write_cache;
+  int pos = 0, seq = 0, slot = 0, q_begin = 0, q_end = 0, page = -1;
+  if (valid) pos = a.token_pos[t];
+  if (to_cache) {
+    seq = a.token_seq[t];
+    slot = a.seq_slot[seq];
+    q_begin = a.seq_qstart[seq];
+    q_end = a.seq_qstart[seq + 1];
+    if (pos >= 0 && pos / kPageTokens < a.table_stride)
+      page = a.page_table[(size_t)slot * a.table_stride + pos / kPageTokens];
+  }
+  const float* w = is_q ? a.q_norm_w : a.k_norm_w;
+  const int rot = a.cos_table ? a.rotary_dim : 0;
+  const int half = rot / 2;
+  const bool rotates = valid && (is_q || is_k);
+  const bool pos_in_table = pos >= 0 && pos < a.table_rows;
+  const float* cs = (rot > 0 && pos_in_table) ? a.cos_table + (size_t)pos * half : nullptr;
+  const float* sn = (rot > 0 && pos_in_table) ? a.sin_table + (size_t)pos * half : nullptr;
+  // the first pair of each lane (PAIRS): angles and weights are on their way before the wait
+  float2 c_first = make_float2(1.f, 1.f), s_first = make_float2(0.f, 0.f);
+  float2 w1_first = make_float2(1.f, 1.f), w2_first = make_float2(1.f, 1.f);
+  if (PAIRS && rotates && lane * 2 < half) {
+    if (cs) {
+      c_first = *reinterpret_cast<const float2*>(cs + lane * 2);
+      s_first = *reinterpret_cast<const float2*>(sn + lane * 2);
+    }
+    if (w) {
+      w1_first = *reinterpret_cast<const float2*>(w + lane * 2);
+      w2_first = *reinterpret_cast<const float2*>(w + lane * 2 + half);
+    }
+  }
+  pdl_wait_block();
+  pdl_launch_dependents();
+  if (!valid) return;
+  T* row = (T*)a.qkv + (size_t)t * a.ld + (size_t)head * d;
 
   // where this token's k/v row lies in the paged cache
   T* cache_row = nullptr;
-  if (!is_q && a.write_cache) {
-    const int slot = a.seq_slot[a.token_seq[t]];
-    const int logical = pos / kPageTokens;
-    if (pos < 0 || logical >= a.table_stride) {
+  if (to_cache) {
+    if (pos < 0 || pos / kPageTokens >= a.table_stride) {
       if (lane == 0) report(a.status, kStatusPositionOutOfRange, t, pos, a.table_stride * kPageTokens);
+    } else if (page < 0 || page >= a.num_pages) {
+      if (lane == 0) report(a.status, kStatusPageOutOfRange, t, page, a.num_pages);
     } else {
-      const int page = a.page_table[(size_t)slot * a.table_stride + logical];
-      if (page < 0 || page >= a.num_pages) {
-        if (lane == 0) report(a.status, kStatusPageOutOfRange, t, page, a.num_pages);
-      } else {
-        T* base = (T*)(is_k ? a.k_pages : a.v_pages);
-        const int off = pos % kPageTokens;
-        cache_row = base + (((size_t)page * a.n_kv_heads + kv_head) * kPageTokens + off) * d;
-        // Rows of a page beyond the sequence's last key must hold finite values (readers multiply them
-        // by a probability of zero): the sequence's last token of this step clears the rest of its page
-        // when it starts the page or ends a multi-token step; later single tokens find it cleared.
-        const int b = a.token_seq[t];
-        const int q_end = a.seq_qstart[b + 1];
-        if (t + 1 == q_end && off + 1 < kPageTokens && (off == 0 || q_end - a.seq_qstart[b] > 1)) {
-          T* rest = cache_row + d;
-          const size_t n = (size_t)(kPageTokens - 1 - off) * d;
-          if ((d * sizeof(T)) % 16 == 0) {
-            uint4* r4 = reinterpret_cast<uint4*>(rest);
-            const size_t n4 = n * sizeof(T) / 16;
-            for (size_t i = lane; i < n4; i += 32) r4[i] = make_uint4(0, 0, 0, 0);
-          } else {
-            for (size_t i = lane; i < n; i += 32) rest[i] = from_f32<T>(0.f);
-          }
+      T* base = (T*)(is_k ? a.k_pages : a.v_pages);
+      const int off = pos % kPageTokens;
+      cache_row = base + (((size_t)page * a.n_kv_heads + kv_head) * kPageTokens + off) * d;
+      // Rows of a page beyond the sequence's last key must hold finite values (readers multiply them
+      // by a probability of zero): the sequence's last token of this step clears the rest of its page
+      // when it starts the page or ends a multi-token step; later single tokens find it cleared.
+      if (t + 1 == q_end && off + 1 < kPageTokens && (off == 0 || q_end - q_begin > 1)) {
+        T* rest = cache_row + d;
+        const size_t n = (size_t)(kPageTokens - 1 - off) * d;
+        if ((d * sizeof(T)) % 16 == 0) {
+          uint4* r4 = reinterpret_cast<uint4*>(rest);
+          const size_t n4 = n * sizeof(T) / 16;
+          for (size_t i = lane; i < n4; i += 32) r4[i] = make_uint4(0, 0, 0, 0);
+        } else {
+          for (size_t i = lane; i < n; i += 32) rest[i] = from_f32<T>(0.f);
         }
       }
     }
@@ -121,7 +149,6 @@ __global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
     return;
   }
 
-  const float* w = is_q ? a.q_norm_w : a.k_norm_w;
   float inv = 1.f;
   if (w) {
     float ss = 0.f;
@@ -146,22 +173,21 @@ __global__ void qk_norm_rope_append_kernel(RopeAppendArgs a) {
     if (w) x = x * inv * w[c];
     return x;
   };
-  const int rot = a.cos_table ? a.rotary_dim : 0;
-  const int half = rot / 2;
-  if (rot > 0 && (pos < 0 || pos >= a.table_rows)) {
+  if (rot > 0 && !pos_in_table) {
     if (lane == 0) report(a.status, kStatusPositionOutOfRange, t, pos, a.table_rows);
     return;
   }
-  const float* cs = a.cos_table ? a.cos_table + (size_t)pos * half : nullptr;
-  const float* sn = a.sin_table ? a.sin_table + (size_t)pos * half : nullptr;
   if (PAIRS) {
     for (int j = lane * 2; j < half; j += 64) {
+      const bool first = j == lane * 2;
       float2 x1 = load2<T>(row + j), x2 = load2<T>(row + j + half);
       if (w) {
-        const float2 w1 = *reinterpret_cast<const float2*>(w + j), w2 = *reinterpret_cast<const float2*>(w + j + half);
+        const float2 w1 = first ? w1_first : *reinterpret_cast<const float2*>(w + j);
+        const float2 w2 = first ? w2_first : *reinterpret_cast<const float2*>(w + j + half);
         x1.x *= inv * w1.x; x1.y *= inv * w1.y; x2.x *= inv * w2.x; x2.y *= inv * w2.y;
       }
-      const float2 c = *reinterpret_cast<const float2*>(cs + j), sv = *reinterpret_cast<const float2*>(sn + j);
+      const float2 c = first ? c_first : *reinterpret_cast<const float2*>(cs + j);
+      const float2 sv = first ? s_first : *reinterpret_cast<const float2*>(sn + j);
       const float2 o1 = make_float2(x1.x * c.x - x2.x * sv.x, x1.y * c.y - x2.y * sv.y);
       const float2 o2 = make_float2(x2.x * c.x + x1.x * sv.x, x2.y * c.y + x1.y * sv.y);
       store2<T>(row + j, o1);
