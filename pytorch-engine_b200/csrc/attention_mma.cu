@@ -509,23 +509,37 @@ __global__ void decode_merge_kernel(Args a) {
   const int win_lo = a.window > 0 ? max(0, len - a.window) : 0;
   const int first = win_lo / per_range;
   const size_t base = ((size_t)b * a.n_heads + h) * a.max_splits;
-  float mx = -INFINITY;
-  for (int s = first; s < n_splits; ++s) mx = fmaxf(mx, a.part_lse[base + s]);
-  float denom = 0.f;
-  for (int s = first; s < n_splits; ++s) {
-    const float e = a.part_lse[base + s];
-    denom += (e == -INFINITY) ? 0.f : expf(e - mx);
-  }
-  const float inv = 1.f / fmaxf(denom, 1e-20f);
   __nv_bfloat16* o = a.out + (size_t)tq * a.out_ld + (size_t)h * HD;
+  // Ranges are taken eight at a time: all their loads are issued before the first is used (this kernel
+  // is short and a decode step waits for it once per layer), then they are folded into a running
+  // maximum, denominator and sum, in range order.
+  constexpr int G = 8;
   for (int c = threadIdx.x; c < HD; c += blockDim.x) {
-    float v = 0.f;
-    for (int s = first; s < n_splits; ++s) {
-      const float e = a.part_lse[base + s];
-      const float w = (e == -INFINITY) ? 0.f : expf(e - mx) * inv;
-      v = fmaf(w, a.part_acc[(base + s) * HD + c], v);
+    float mx = -INFINITY, denom = 0.f, v = 0.f;
+    for (int s0 = first; s0 < n_splits; s0 += G) {
+      float e[G], acc[G];
+#pragma unroll
+      for (int i = 0; i < G; ++i) {
+        const bool live = s0 + i < n_splits;
+        e[i] = live ? a.part_lse[base + s0 + i] : -INFINITY;
+        acc[i] = live ? a.part_acc[(base + s0 + i) * HD + c] : 0.f;
+      }
+      float m_new = mx;
+#pragma unroll
+      for (int i = 0; i < G; ++i) m_new = fmaxf(m_new, e[i]);
+      if (m_new == -INFINITY) continue;
+      const float keep = (mx == -INFINITY) ? 0.f : expf(mx - m_new);
+      denom *= keep;
+      v *= keep;
+#pragma unroll
+      for (int i = 0; i < G; ++i) {
+        const float w = (e[i] == -INFINITY) ? 0.f : expf(e[i] - m_new);
+        denom += w;
+        v = fmaf(w, acc[i], v);
+      }
+      mx = m_new;
     }
-    o[c] = __float2bfloat16_rn(v);
+    o[c] = __float2bfloat16_rn(v / fmaxf(denom, 1e-20f));
   }
 }
 
