@@ -42,9 +42,9 @@ def test_embed_gather(ops, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("dim", [80, 1000, 4096, 5120])
-def test_rmsnorm_with_residual(ops, dtype, dim):
+@pytest.mark.parametrize("n", [7, 100])    # a handful of rows get more threads a row than many rows do
+def test_rmsnorm_with_residual(ops, dtype, dim, n):
     torch.manual_seed(1)
-    n = 7
     res = torch.randn(n, dim, device=DEV) * 3
     delta = torch.randn(n, dim, device=DEV).to(dtype)
     w = 1 + 0.1 * torch.randn(dim, device=DEV)
