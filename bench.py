@@ -191,12 +191,15 @@ def main():
             engine.cache.commit(s, start_len)
         toks = torch.randint(0, vocab, (steps + warmup, batch), generator=gen).tolist()
         reqs = list(range(batch))
+        # the sampler as the engine runs it: rows cut into chunks by a first kernel (it needs a scratch)
+        need = ops.sample_scratch_bytes(batch, vocab, 0.0, 0, 1.0, 0.0)
+        scratch = torch.empty(need, dtype=torch.uint8, device=engine.device) if need else None
 
         def one(i):
             logits = engine.runner.step([pe.StepEntry(s, (toks[i][j],), (0,)) for j, s in enumerate(slots)], check=False)
             meta = torch.tensor([reqs, [i] * batch], dtype=torch.int32).to(engine.device, non_blocking=True)
             out = torch.empty((batch,), dtype=torch.int32, device=engine.device)
-            ops.sample(logits, 0.0, 0, 1.0, 0.0, 0, meta[0], meta[1], out)
+            ops.sample(logits, 0.0, 0, 1.0, 0.0, 0, meta[0], meta[1], out, scratch=scratch)
             return out
 
         for i in range(warmup):
