@@ -122,6 +122,35 @@ def prefill_flops(cfg, layers, tokens):
     return 2 * tokens * layers * n["linear_params_per_layer"] + layers * n["attn_flops_per_layer"](tokens) + 2 * n["head_params"]
 
 
+def reference_arm(args):
+    """``--impl reference``: the unmodified reference through its own public API (baseline/reference_arm.py,
+    which imports nothing of this repository's package), same metric, same sizes, same JSON keys."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import reference_arm as arm
+
+        with open(os.path.join(ROOT, "pytorch-engine_b200", "config", "presets", args.preset + ".json")) as fh:
+            cfg = json.load(fh)
+        out = arm.run(cfg, preset_name=args.preset, batch=args.batch, context=args.context, steps=args.steps,
+                      warmup=args.warmup, layers=args.layers)
+    except BaseException as exc:  # the arm says why it cannot run; it never fails the benchmark
+        if isinstance(exc, KeyboardInterrupt):
+            raise
+        text = str(exc).strip().splitlines()
+        out = {"impl": "reference", "unavailable": f"{type(exc).__name__}: {text[0][:300] if text else ''}"}
+    print(json.dumps(out))
+    return 0
+
+
+def plain_torch_baseline(cfg_dict, layers, args):
+    """The plain PyTorch model of the same shape on the same GPU (baseline/plain_torch.py: library calls only)."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import plain_torch
+
+    return plain_torch.measure(cfg_dict, layers, context=args.context, batches=sorted({1, args.batch, 64}),
+                               prefill_tokens=0 if args.no_prefill else args.prefill_tokens)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -137,20 +166,18 @@ def main():
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-cuda-graph", action="store_true")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the plain PyTorch model that vs_baseline divides by")
     ap.add_argument("--micro", type=str, default=None,
                     help="time single kernels at the preset's sizes instead (gemm, prefill_attention, decode_attention, sampler) and print text")
     args = ap.parse_args()
 
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is not an installable package (pip: neither setup.py nor pyproject.toml found), "
-                          "it has no batching and no bfloat16 path, and it loads GGUF files only"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.impl == "reference":
+        return reference_arm(args)
 
     import torch
 
@@ -299,6 +326,17 @@ def main():
         out["e2e"] = {"value": round(n_tokens / dt, 2), "unit": "tokens/s", "tokens": n_tokens,
                       "h2d_bytes_per_step": (B + 3 * B + 1 + B) * 4 + 2 * B * 4, "d2h_bytes_per_step": B * 4 + 16,
                       "api": "Engine.stream_tokens, greedy, prompts of %d tokens, %d untimed steps" % (plen, W)}
+
+    if not args.no_baseline:
+        # the same shape as a plain PyTorch model (library products and attention, eager) on this GPU
+        base = plain_torch_baseline(cfg.to_dict(), layers, args)
+        out["baseline"] = {"what": "plain PyTorch (F.linear bf16, scaled_dot_product_attention, eager, contiguous cache), same GPU"}
+        for k, v in base.items():
+            out["baseline"][k] = v["tokens_per_s"]
+        mine = base.get(f"decode_b{B}")
+        if mine:
+            out["vs_baseline"] = round(value / mine["tokens_per_s"], 3)
+            out["baseline"]["ms_per_step"] = mine["ms_per_step"]
 
     print(json.dumps(out))
     return 0

@@ -61,7 +61,7 @@ def qwen3_plan(cfg: Qwen3Config) -> ModelPlan:
                 "down_proj": f"{p}.mlp.down_proj.weight",
             },
         )
-        blocks.append(BlockSpec(
+        blocks.append(BlockSpec.standard(
             arrangement="pre_norm",
             mixer_norm=norm(f"{p}.input_layernorm.weight"),
             mixer=mixer,
@@ -82,6 +82,9 @@ def qwen3_plan(cfg: Qwen3Config) -> ModelPlan:
         head=PartSpec("linear_head", {"vocab": cfg.vocab_size, "hidden": h}, {"weight": head_name}),
         positions={"rope": PartSpec("rope", {"rotary_dim": cfg.head_dim, "theta": cfg.rope_theta,
                                              "max_positions": cfg.max_position_embeddings, "style": "neox"})},
+        # published tied checkpoints may store the head a second time; stored rotary frequencies carry no weights
+        duplicates={"lm_head.weight": embed_name} if cfg.tie_word_embeddings else {},
+        ignored=("*.rotary_emb.inv_freq",),
     )
 
 

@@ -74,7 +74,7 @@ class CacheGroup:
 
 
 class PagedCache:
-    def __init__(self, requests: Mapping[int, Optional[CacheRequest]], *, max_tokens: int, max_slots: int,
+    def __init__(self, requests: Mapping[object, Optional[CacheRequest]], *, max_tokens: int, max_slots: int,
                  max_seq_len: int, dtype: torch.dtype, device) -> None:
         if max_tokens <= 0 or max_slots <= 0 or max_seq_len <= 0:
             raise ValueError("max_tokens, max_slots and max_seq_len must be positive")
@@ -87,9 +87,9 @@ class PagedCache:
         self.slots = NumberPool(max_slots, "slot")
         self.lengths: Dict[int, int] = {}
         self.groups: List[CacheGroup] = []
-        self._entry: Dict[int, Tuple[int, int]] = {}  # entry id -> (group number, index in group)
+        self._entry: Dict[object, Tuple[int, int]] = {}  # entry key (int, or (int, mixer name)) -> (group number, index in group)
         by_key: Dict[tuple, int] = {}
-        for entry_id in sorted(requests):
+        for entry_id in sorted(requests, key=lambda e: e if isinstance(e, tuple) else (e, "")):
             req = requests[entry_id]
             if req is None:
                 continue
@@ -127,7 +127,7 @@ class PagedCache:
         else:
             raise ValueError(f"unknown cache kind {r.kind!r} (known: 'kv', 'state')")
 
-    def view(self, entry_id: int) -> Optional[CacheView]:
+    def view(self, entry_id) -> Optional[CacheView]:
         if entry_id not in self._entry:
             return None
         gi, idx = self._entry[entry_id]

@@ -101,7 +101,7 @@ class Engine:
         self.plan = arch.plan(config)
         self.runtime = Runtime(self.device, self.dtype)
         if weights is None:
-            weights = load_weights(model_path, self.plan, device=self.device)
+            weights = load_weights(model_path, self.plan, device=self.device, dtype=self.dtype)
         self.model = DecoderModel(self.plan, weights, self.runtime)
         del weights
         self.max_context_len = int(max_context_len or config.max_positions)

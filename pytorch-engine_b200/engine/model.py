@@ -35,13 +35,11 @@ class DecoderModel:
         self.positions = {name: _build_part("position", spec, weights, runtime) for name, spec in plan.positions.items()}
         self.embedding = _build_part("embedding", plan.embedding, weights, runtime)
         self.blocks = []
+        self.block_parts = []     # per block: {part name: built part}
         for b in plan.blocks:
-            parts = {
-                "mixer_norm": _build_part("norm", b.mixer_norm, weights, runtime),
-                "mixer": _build_part("mixer", b.mixer, weights, runtime, positions=self.positions),
-                "ffn_norm": _build_part("norm", b.ffn_norm, weights, runtime),
-                "ffn": _build_part("feed_forward", b.ffn, weights, runtime),
-            }
+            parts = {name: _build_part(role, spec, weights, runtime, positions=self.positions)
+                     for name, (role, spec) in b.parts.items()}
+            self.block_parts.append(parts)
             self.blocks.append(lookup("arrangement", b.arrangement)(b, parts, runtime))
         self.final_norm = _build_part("norm", plan.final_norm, weights, runtime)
         self.head = _build_part("head", plan.head, weights, runtime)
@@ -51,24 +49,46 @@ class DecoderModel:
         """Whether a step may be recorded into a CUDA graph: every part must say so itself
         (``graph_safe = True``); a part that reads device memory on the host during its forward cannot."""
         parts = [self.embedding, self.final_norm, self.head, *self.positions.values()]
-        for b in self.blocks:
-            parts.append(b)
-            parts.extend(getattr(b, name) for name in ("mixer_norm", "mixer", "ffn_norm", "ffn") if hasattr(b, name))
+        for block, built in zip(self.blocks, self.block_parts):
+            parts.append(block)
+            parts.extend(built.values())
         return all(getattr(p, "graph_safe", False) for p in parts)
 
-    def cache_requests(self) -> Dict[int, Optional[CacheRequest]]:
-        """Cache entry id -> what the mixer that writes it needs."""
-        reqs: Dict[int, Optional[CacheRequest]] = {}
+    @staticmethod
+    def cache_key(entry: int, block_spec, mixer_name: str):
+        """The cache's key for one mixer of a run: the entry number itself for a block with one mixer,
+        ``(entry, mixer name)`` for a block with several."""
+        return entry if len(block_spec.mixer_names()) <= 1 else (entry, mixer_name)
+
+    def cache_requests(self) -> Dict[object, Optional[CacheRequest]]:
+        """Cache key -> what the mixer that writes it needs."""
+        reqs: Dict[object, Optional[CacheRequest]] = {}
+        written = set()
         for run in self.plan.order:
-            if not run.writes_cache or run.cache_entry in reqs:
+            if not run.writes_cache or run.cache_entry in written:
                 continue
-            spec = self.plan.blocks[run.block].mixer
-            cls = lookup("mixer", spec.kind)
-            reqs[run.cache_entry] = cls.cache_request(spec.params) if hasattr(cls, "cache_request") else None
+            written.add(run.cache_entry)
+            b = self.plan.blocks[run.block]
+            for name in b.mixer_names():
+                spec = b.part(name)
+                cls = lookup("mixer", spec.kind)
+                reqs[self.cache_key(run.cache_entry, b, name)] = (
+                    cls.cache_request(spec.params) if hasattr(cls, "cache_request") else None)
         for run in self.plan.order:
-            if run.cache_entry not in reqs:
+            if run.cache_entry not in written:
                 raise ValueError(f"block {run.block} reads cache entry {run.cache_entry}, which no block writes")
         return reqs
+
+    def _view(self, cache, run):
+        """What a block's arrangement gets as its cache view: the view of its one mixer, a dict of
+        views by mixer name for a block with several, None for a block without a mixer."""
+        b = self.plan.blocks[run.block]
+        names = b.mixer_names()
+        if not names:
+            return None
+        if len(names) == 1:
+            return cache.view(run.cache_entry)
+        return {name: cache.view((run.cache_entry, name)) for name in names}
 
     def forward(self, ctx, cache) -> torch.Tensor:
         """Run the step described by ``ctx``; returns float32 logits ``[n_want, vocab]``."""
@@ -77,7 +97,7 @@ class DecoderModel:
         self.embedding.forward(ctx.tokens, stream)
         pending = None
         for run in self.plan.order:
-            view = cache.view(run.cache_entry)
+            view = self._view(cache, run)
             block = self.blocks[run.block]
             if run.writes_cache:
                 pending = block.forward(stream, pending, ctx, view)
@@ -105,7 +125,7 @@ class DecoderModel:
         visit(self.head)
         for p in self.positions.values():
             visit(p)
-        for b in self.blocks:
-            for part in (b.mixer_norm, b.mixer, b.ffn_norm, b.ffn) if hasattr(b, "mixer_norm") else ():
+        for built in self.block_parts:
+            for part in built.values():
                 visit(part)
         return total

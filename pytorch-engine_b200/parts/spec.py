@@ -2,8 +2,8 @@
 
 An architecture turns its typed configuration into a ``ModelPlan``.  The plan is plain data:
 every part is a ``PartSpec`` (a registry key, the part's sizes and constants, and the checkpoint
-tensor name of each of its weights); a block is an arrangement of two norms, a mixer and a
-feed-forward; and the order in which blocks run is a list of ``RunStep`` entries, which may name
+tensor name of each of its weights); a block is an arrangement and the named parts it wires (usually
+two norms, a mixer and a feed-forward); and the order in which blocks run is a list of ``RunStep`` entries, which may name
 a block twice or let a block use the cache entry of another one.  Nothing in ``parts/`` knows
 which model it is part of: the generic decoder (``engine/model.py``) builds whatever the plan
 says by looking the kinds up in ``parts/registry.py``.
@@ -26,16 +26,31 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class BlockSpec:
-    """A residual block.  ``arrangement`` names how norms, mixer and feed-forward are wired
-    (registry of block arrangements); the four parts are chosen independently, so two blocks of
-    one model may differ in any of them."""
+    """A residual block: an ``arrangement`` (registry of block arrangements: how the parts are wired
+    around the residual stream) and the parts themselves, by name: ``parts[name] = (role, PartSpec)``
+    with ``role`` one of "norm", "mixer", "feed_forward".  The arrangement decides which names it
+    wants; a block may carry four norms, two mixers or no feed-forward.  Every part is chosen
+    independently, so two blocks of one model may differ in any of them.
+
+    ``BlockSpec.standard`` builds the usual block of two norms, a mixer and a feed-forward under
+    the names ``mixer_norm, mixer, ffn_norm, ffn``."""
 
     arrangement: str
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    ffn_norm: PartSpec
-    ffn: PartSpec
+    parts: Mapping[str, Tuple[str, PartSpec]]
     name: str = ""
+
+    @classmethod
+    def standard(cls, arrangement: str, mixer_norm: PartSpec, mixer: PartSpec, ffn_norm: PartSpec, ffn: PartSpec,
+                 name: str = "") -> "BlockSpec":
+        return cls(arrangement, {"mixer_norm": ("norm", mixer_norm), "mixer": ("mixer", mixer),
+                                 "ffn_norm": ("norm", ffn_norm), "ffn": ("feed_forward", ffn)}, name)
+
+    def part(self, name: str) -> PartSpec:
+        return self.parts[name][1]
+
+    def mixer_names(self) -> Tuple[str, ...]:
+        """Names of the parts that are mixers, in the order the block lists them."""
+        return tuple(n for n, (role, _) in self.parts.items() if role == "mixer")
 
 
 @dataclass(frozen=True)
@@ -65,6 +80,11 @@ class ModelPlan:
     head: PartSpec
     # position encodings by name; a mixer names the one it uses in params["position"]
     positions: Mapping[str, PartSpec] = field(default_factory=dict)
+    # checkpoint names that a file may hold beside the plan's own: ``duplicates[name] = other`` accepts
+    # ``name`` if it equals tensor ``other`` (a tied head stored twice); ``ignored`` are name patterns
+    # (``fnmatch``) of stored buffers that carry no weights
+    duplicates: Mapping[str, str] = field(default_factory=dict)
+    ignored: Tuple[str, ...] = ()
 
     def part_specs(self):
         """Every PartSpec of the plan as (label, role, spec), for the weight loader and error texts."""
@@ -73,10 +93,8 @@ class ModelPlan:
             yield f"position {name}", "position", spec
         for i, b in enumerate(self.blocks):
             label = b.name or f"block {i}"
-            yield f"{label} mixer_norm", "norm", b.mixer_norm
-            yield f"{label} mixer", "mixer", b.mixer
-            yield f"{label} ffn_norm", "norm", b.ffn_norm
-            yield f"{label} ffn", "feed_forward", b.ffn
+            for name, (role, spec) in b.parts.items():
+                yield f"{label} {name}", role, spec
         yield "final_norm", "norm", self.final_norm
         yield "head", "head", self.head
 

@@ -234,9 +234,15 @@ def load_folder(folder: str):
     with open(os.path.join(folder, "config.json")) as fh:
         cfg = json.load(fh)
     tensors: Dict[str, torch.Tensor] = {}
-    with safe_open(os.path.join(folder, "model.safetensors"), framework="pt", device="cpu") as fh:
-        for name in fh.keys():
-            tensors[name] = fh.get_tensor(name)
+    index = os.path.join(folder, "model.safetensors.index.json")
+    files = ["model.safetensors"]
+    if os.path.isfile(index):                       # a folder written in shards
+        with open(index) as fh:
+            files = sorted(set(json.load(fh)["weight_map"].values()))
+    for fname in files:
+        with safe_open(os.path.join(folder, fname), framework="pt", device="cpu") as fh:
+            for name in fh.keys():
+                tensors[name] = fh.get_tensor(name)
     return cfg, tensors
 
 

@@ -73,8 +73,8 @@ def test_plan_is_data(pe):
     cfg = pe.Qwen3Config.from_dict(TEST_CONFIGS["B"])
     plan = pe.config.architecture(cfg.architecture).plan(cfg)
     assert len(plan.blocks) == 3 and [r.block for r in plan.order] == [0, 1, 2]
-    assert plan.blocks[0].mixer.params["window"] is None and plan.blocks[2].mixer.params["window"] == 40
-    assert plan.blocks[1].mixer.params["head_dim"] == 32 and plan.blocks[1].ffn.params["intermediate"] == 200
+    assert plan.blocks[0].part("mixer").params["window"] is None and plan.blocks[2].part("mixer").params["window"] == 40
+    assert plan.blocks[1].part("mixer").params["head_dim"] == 32 and plan.blocks[1].part("ffn").params["intermediate"] == 200
     assert plan.head.weights["weight"] == "lm_head.weight"
     tied = pe.config.architecture(cfg.architecture).plan(pe.Qwen3Config.from_dict(TEST_CONFIGS["A"]))
     assert tied.head.weights["weight"] == tied.embedding.weights["weight"]

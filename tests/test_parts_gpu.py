@@ -144,12 +144,12 @@ def test_block_arrangement_alone(pe, dtype):
     lookup = pe.parts.lookup
     pick = lambda part: {k: w[v] for k, v in part.weights.items()}
     rope = lookup("position", "rope")(plan.positions["rope"].params, {}, rt)
-    parts = {"mixer_norm": lookup("norm", spec.mixer_norm.kind)(spec.mixer_norm.params, pick(spec.mixer_norm), rt),
-             "mixer": lookup("mixer", spec.mixer.kind)(spec.mixer.params, pick(spec.mixer), rt, positions={"rope": rope}),
-             "ffn_norm": lookup("norm", spec.ffn_norm.kind)(spec.ffn_norm.params, pick(spec.ffn_norm), rt),
-             "ffn": lookup("feed_forward", spec.ffn.kind)(spec.ffn.params, pick(spec.ffn), rt)}
+    parts = {}
+    for name, (role, part) in spec.parts.items():
+        extra = {"positions": {"rope": rope}} if role == "mixer" else {}
+        parts[name] = lookup(role, part.kind)(part.params, pick(part), rt, **extra)
     block = lookup("arrangement", spec.arrangement)(spec, parts, rt)
-    cache = pe.cache.PagedCache({1: lookup("mixer", "attention").cache_request(spec.mixer.params)}, max_tokens=256,
+    cache = pe.cache.PagedCache({1: lookup("mixer", "attention").cache_request(spec.part("mixer").params)}, max_tokens=256,
                                 max_slots=2, max_seq_len=256, dtype=dtype, device=DEV)
     slot = cache.alloc_slot()
     S = 70
@@ -228,7 +228,7 @@ def test_toy_mixer_with_state_of_its_own(pe):
     def plan(cfg):
         h = cfg.hidden_size
         norm = lambda n: P("rmsnorm", {"dim": h, "eps": 1e-6}, {"weight": n})
-        blocks = tuple(B("pre_norm", norm(f"l{i}.n1"), P("decaying_sum", {"hidden": h, "decay": cfg.decay}, {"proj": f"l{i}.proj"}),
+        blocks = tuple(B.standard("pre_norm", norm(f"l{i}.n1"), P("decaying_sum", {"hidden": h, "decay": cfg.decay}, {"proj": f"l{i}.proj"}),
                          norm(f"l{i}.n2"), P("swiglu", {"hidden": h, "intermediate": 2 * h},
                                              {"gate_proj": f"l{i}.g", "up_proj": f"l{i}.u", "down_proj": f"l{i}.d"}),
                          name=f"toy {i}") for i in range(cfg.layers))
@@ -448,8 +448,8 @@ def test_toy_routed_feed_forward_and_another_position_encoding(pe):
         routed = P("top_one_experts", {"hidden": h, "experts": cfg.experts, "expert_size": cfg.expert_size},
                    {"router": "l0.router", **{f"{k}{x}": f"l0.{k}{x}" for x in range(cfg.experts) for k in ("gate", "up", "down")}})
         dense = P("swiglu", {"hidden": h, "intermediate": 2 * h}, {"gate_proj": "l1.g", "up_proj": "l1.u", "down_proj": "l1.d"})
-        blocks = (B("pre_norm", norm("l0.n1"), att(0, "slow"), norm("l0.n2"), routed, name="routed"),
-                  B("pre_norm", norm("l1.n1"), att(1, "rope"), norm("l1.n2"), dense, name="dense"))
+        blocks = (B.standard("pre_norm", norm("l0.n1"), att(0, "slow"), norm("l0.n2"), routed, name="routed"),
+                  B.standard("pre_norm", norm("l1.n1"), att(1, "rope"), norm("l1.n2"), dense, name="dense"))
         return pe.parts.ModelPlan(
             hidden_size=h, vocab_size=cfg.vocab_size, max_positions=cfg.max_position_embeddings,
             embedding=P("token_embedding", {"vocab": cfg.vocab_size, "hidden": h}, {"weight": "emb"}),
@@ -544,8 +544,8 @@ def test_toy_block_arrangement(pe):
                                         "qk_norm": False, "eps": eps, "scale": None, "window": None, "position": "rope"},
                           {k: f"l{i}.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj")})
         ffn = lambda i: P("swiglu", {"hidden": h, "intermediate": 2 * h}, {"gate_proj": f"l{i}.g", "up_proj": f"l{i}.u", "down_proj": f"l{i}.d"})
-        blocks = (B("parallel", norm("l0.n1"), att(0), norm("l0.n2"), ffn(0), name="parallel"),
-                  B("pre_norm", norm("l1.n1"), att(1), norm("l1.n2"), ffn(1), name="sequential"))
+        blocks = (B.standard("parallel", norm("l0.n1"), att(0), norm("l0.n2"), ffn(0), name="parallel"),
+                  B.standard("pre_norm", norm("l1.n1"), att(1), norm("l1.n2"), ffn(1), name="sequential"))
         return pe.parts.ModelPlan(
             hidden_size=h, vocab_size=c.vocab_size, max_positions=c.max_position_embeddings,
             embedding=P("token_embedding", {"vocab": c.vocab_size, "hidden": h}, {"weight": "emb"}),
@@ -637,7 +637,7 @@ def test_toy_norm(pe):
         return pe.parts.ModelPlan(
             hidden_size=h, vocab_size=c.vocab_size, max_positions=c.max_position_embeddings,
             embedding=P("token_embedding", {"vocab": c.vocab_size, "hidden": h}, {"weight": "emb"}),
-            blocks=(B("pre_norm", norm("l0.n1"), att, norm("l0.n2"), ffn, name="only"),), order=(R(0),),
+            blocks=(B.standard("pre_norm", norm("l0.n1"), att, norm("l0.n2"), ffn, name="only"),), order=(R(0),),
             final_norm=norm("fn"), head=P("linear_head", {"vocab": c.vocab_size, "hidden": h}, {"weight": "head"}),
             positions={"rope": P("rope", {"rotary_dim": d, "theta": theta, "max_positions": c.max_position_embeddings})})
 
