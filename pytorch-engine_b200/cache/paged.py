@@ -254,6 +254,13 @@ class PagedCache:
             del pages[keep:]
         self.lengths[slot] = length
 
+    def reset(self) -> None:
+        """Give every live slot back at once: all sequences are forgotten, every page is free again (the
+        reference's ``clear``, pygguf_engine/kv_cache.py:2644).  Storage is not touched: nothing reads beyond a
+        sequence's length, and state is zeroed when a slot is taken."""
+        for slot in self.live_slots:
+            self.free_slot(slot)
+
     def check(self) -> None:
         """Bookkeeping invariants: no page lost, held twice, or held by a slot that is not live."""
         self.slots.check()

@@ -17,7 +17,7 @@ from typing import List
 
 
 def build_parser() -> argparse.ArgumentParser:
-    p = argparse.ArgumentParser(prog="pytorch-engine_b200", description="Generate tokens on one B200 (Qwen3 dense)")
+    p = argparse.ArgumentParser(prog="pytorch-engine_b200", description="Generate tokens on one B200 from a model folder or a random model of a named size")
     src = p.add_argument_group("model")
     src.add_argument("--model", type=str, default=None, help="folder with config.json and model.safetensors")
     src.add_argument("--random", type=str, default=None, metavar="PRESET",

@@ -18,6 +18,7 @@ from dataclasses import dataclass, field
 from typing import Any, Dict, Optional, Tuple
 
 from .base import ConfigError, ModelConfig, require_float, require_int
+from .registry import register_preset_folder
 
 
 @dataclass(frozen=True)
@@ -186,20 +187,5 @@ class Qwen3Config(ModelConfig):
         return self.sliding_window if layer >= self.max_window_layers else None
 
 
-# Named size presets are config.json files under ``presets/`` beside this module (random-weights
-# mode and the benchmark read them); no size stands in code.
-_PRESET_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "presets")
-
-
-def preset_names():
-    return sorted(f[:-5] for f in os.listdir(_PRESET_DIR) if f.endswith(".json"))
-
-
-def preset(name: str, **overrides: Any) -> Qwen3Config:
-    path = os.path.join(_PRESET_DIR, name + ".json")
-    if not os.path.isfile(path):
-        raise ConfigError(f"unknown preset {name!r}; known: {', '.join(preset_names())}")
-    with open(path) as fh:
-        d = json.load(fh)
-    d.update(overrides)
-    return Qwen3Config.from_dict(d)
+# This architecture's named sizes: config.json files under ``presets/`` beside this module.
+register_preset_folder(os.path.join(os.path.dirname(os.path.abspath(__file__)), "presets"))

@@ -8,8 +8,10 @@ pygguf_engine/gguf_parser.py:397); this table replaces those branches.
 """
 from __future__ import annotations
 
+import json
+import os
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Type
+from typing import Any, Callable, Dict, List, Type
 
 from .base import ConfigError, ModelConfig, read_config_dict
 
@@ -59,4 +61,49 @@ def architecture_of(config_dict: Dict[str, Any]) -> Architecture:
 def load_config(folder: str) -> ModelConfig:
     """Typed configuration of a model folder, class chosen by ``architectures[0]``."""
     d = read_config_dict(folder)
+    return architecture_of(d).config_class.from_dict(d)
+
+
+# ---- named presets ---------------------------------------------------------------------------------
+# A preset is a config.json under another name: ``<folder>/<name>.json``.  Which configuration class reads
+# it is decided by its own ``architectures[0]``, as for a model folder, so an architecture brings its presets
+# by registering a folder; no size stands in code.
+_PRESET_FOLDERS: List[str] = []
+
+
+def register_preset_folder(folder: str) -> None:
+    """Make every ``*.json`` of ``folder`` a preset (``--random NAME``, ``preset(NAME)``)."""
+    folder = os.path.abspath(folder)
+    if folder not in _PRESET_FOLDERS:
+        _PRESET_FOLDERS.append(folder)
+
+
+def unregister_preset_folder(folder: str) -> None:
+    folder = os.path.abspath(folder)
+    if folder in _PRESET_FOLDERS:
+        _PRESET_FOLDERS.remove(folder)
+
+
+def _preset_files() -> Dict[str, str]:
+    found: Dict[str, str] = {}
+    for folder in _PRESET_FOLDERS:
+        if os.path.isdir(folder):
+            for f in sorted(os.listdir(folder)):
+                if f.endswith(".json"):
+                    found.setdefault(f[:-5], os.path.join(folder, f))
+    return found
+
+
+def preset_names():
+    return sorted(_preset_files())
+
+
+def preset(name: str, **overrides: Any) -> ModelConfig:
+    """The typed configuration of preset ``name``; ``overrides`` replace keys of its JSON first."""
+    files = _preset_files()
+    if name not in files:
+        raise ConfigError(f"unknown preset {name!r}; known: {', '.join(sorted(files)) or 'none'}")
+    with open(files[name]) as fh:
+        d = json.load(fh)
+    d.update(overrides)
     return architecture_of(d).config_class.from_dict(d)

@@ -276,9 +276,15 @@ __global__ void attn_decode_combine_kernel(AttnArgs a) {
   const int d = a.head_dim;
   const int t = a.seq_qstart[b];
   const int len = a.seq_past[b] + 1;
-  const int n_splits = (len + a.split_keys - 1) / a.split_keys;
+  int n_splits = (len + a.split_keys - 1) / a.split_keys;
+  if (n_splits > a.max_splits) {
+    // the sequence is longer than split_keys * max_splits keys: the split grid has no block for the ranges
+    // beyond, and the scratch no room for them; say so and merge what was computed
+    if (threadIdx.x == 0) report(a.status, kStatusPositionOutOfRange, b, len - 1, a.split_keys * a.max_splits);
+    n_splits = a.max_splits;
+  }
   const int win_lo = a.window > 0 ? max(0, len - a.window) : 0;
-  const int first = win_lo / a.split_keys;
+  const int first = min(win_lo / a.split_keys, n_splits);
   const size_t base = ((size_t)b * a.n_heads + h) * a.max_splits;
   float mx = -INFINITY;
   for (int s = first; s < n_splits; ++s) mx = fmaxf(mx, a.part_lse[base + s]);

@@ -505,9 +505,15 @@ __global__ void decode_merge_kernel(Args a) {
   const int tq = a.seq_qstart[b];
   const int len = a.seq_past[b] + 1;
   const int per_range = range_keys(a, len);
-  const int n_splits = (len + per_range - 1) / per_range;
+  int n_splits = (len + per_range - 1) / per_range;
+  if (n_splits > a.max_splits) {
+    // only with a fixed split_keys: the sequence is longer than split_keys * max_splits keys, for which the
+    // split grid has no blocks and the scratch no room; say so and merge what was computed
+    if (threadIdx.x == 0) report(a.status, kStatusPositionOutOfRange, b, len - 1, per_range * a.max_splits);
+    n_splits = a.max_splits;
+  }
   const int win_lo = a.window > 0 ? max(0, len - a.window) : 0;
-  const int first = win_lo / per_range;
+  const int first = min(win_lo / per_range, n_splits);
   const size_t base = ((size_t)b * a.n_heads + h) * a.max_splits;
   __nv_bfloat16* o = a.out + (size_t)tq * a.out_ld + (size_t)h * HD;
   // Ranges are taken eight at a time: all their loads are issued before the first is used (this kernel

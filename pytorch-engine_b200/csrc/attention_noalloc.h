@@ -13,6 +13,10 @@
 //     every GPU on which the library is used keeps those 8 MiB until the process exits.
 //   * A call needs n_seqs * n_heads * max_splits * (head_dim + 1) floats.  A call that needs more
 //     is refused with PE_ERR_SCRATCH_TOO_LARGE and launches nothing.
+//   * Every sequence must fit its ranges: seq_past[b] + 1 <= split_keys * max_splits.  The lengths live on
+//     the device, so the host cannot check this before the launch; the kernel does.  For a longer sequence
+//     it sets the status word (code 3: sequence index, last position, the limit), reads nothing outside the
+//     array and writes the attention over the first split_keys * max_splits keys only.
 //   * The first call on a device looks up the array's device address (cudaGetSymbolAddress, once per
 //     device, with that device current).  Make that first call outside any stream capture.
 //   * The function calls no cudaMalloc, cudaFree or other allocating routine.

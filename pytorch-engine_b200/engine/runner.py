@@ -74,7 +74,10 @@ class ModelRunner:
             logits = self._step_graph(ints, n_seqs)
         else:
             ctx = StepContext(self.runtime, self.pool, n_tokens=n_tokens, n_seqs=n_seqs, max_q=max(q_lens),
-                              decode=decode, max_kv_len=max(p + q for p, q in zip(pasts, q_lens)), n_want=n_want)
+                              decode=decode, n_want=n_want,
+                              # decode: the longest sequence the cache allows, as in the captured graphs, so that how a
+                              # sequence's keys are cut into ranges never depends on the other sequences' lengths
+                              max_kv_len=self.cache.max_seq_len if decode else max(p + q for p, q in zip(pasts, q_lens)))
             self.stager.send(ints, ctx.meta)
             ops.batch_expand(ctx.seq_qstart, ctx.seq_past, n_seqs, ctx.token_seq, ctx.token_pos)
             logits = self.model.forward(ctx, self.cache)
@@ -128,8 +131,10 @@ class ModelRunner:
         return g.logits
 
     def _capture(self, host_meta: torch.Tensor, n_seqs: int) -> _DecodeGraph:
-        """Capture one decode step for exactly ``n_seqs`` sequences.  The capture itself runs the
-        step once eagerly first (warm-up: library handles, kernel attributes), then records it."""
+        """Capture one decode step for exactly ``n_seqs`` sequences.  The step runs exactly once, eagerly
+        (which also warms up library handles and kernel attributes): recording it into the graph afterwards
+        executes nothing, and the eager run's logits are handed over to the graph's output buffer.  So a mixer
+        that folds each token into a state of fixed size sees this step's tokens once, as in every other step."""
         pool = BufferPool(self.runtime.device)
         ctx = StepContext(self.runtime, pool, n_tokens=n_seqs, n_seqs=n_seqs, max_q=1, decode=True,
                           max_kv_len=self.cache.max_seq_len, n_want=n_seqs)
@@ -138,7 +143,7 @@ class ModelRunner:
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
             ops.batch_expand(ctx.seq_qstart, ctx.seq_past, n_seqs, ctx.token_seq, ctx.token_pos)
-            self.model.forward(ctx, self.cache)  # warm-up; writes the same cache rows the capture run will
+            eager_logits = self.model.forward(ctx, self.cache)  # the step itself
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize(self.runtime.device)
         graph = torch.cuda.CUDAGraph()
@@ -147,7 +152,8 @@ class ModelRunner:
             ops.batch_expand(ctx.seq_qstart, ctx.seq_past, n_seqs, ctx.token_seq, ctx.token_pos)
             logits = self.model.forward(ctx, self.cache)
         launches = ops.launch_count() - before
-        graph.replay()
+        if logits.data_ptr() != eager_logits.data_ptr():
+            logits.copy_(eager_logits)
         g = _DecodeGraph(graph, ctx, logits, pool, launches)
         self._graphs[n_seqs] = g
         return g

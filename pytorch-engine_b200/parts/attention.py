@@ -72,11 +72,15 @@ class GQAttention:
             self.q_norm = runtime.adopt(weights["q_norm"], torch.float32)
             self.k_norm = runtime.adopt(weights["k_norm"], torch.float32)
         self.position = None
+        self.fused_position = False
         name = params.get("position")
         if name is not None:
             self.position = (positions or {})[name]
-            if not getattr(self.position, "fusable_rotary", False):
-                raise ValueError(f"position encoding {name!r} cannot be fused into attention (needs tables())")
+            # a rotary encoding with tables is fused into the q/k-norm + append kernel; any other one is
+            # applied by its own ``apply(q, k, positions)`` between that kernel's norm and its append
+            self.fused_position = bool(getattr(self.position, "fusable_rotary", False))
+            if not self.fused_position and not hasattr(self.position, "apply"):
+                raise ValueError(f"position encoding {name!r} offers neither tables() nor apply(q, k, positions)")
         self.qkv_dim = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
         # tensor-core kernels where they take the shape (bfloat16, head size 64 or 128, group <= 16);
         # the generic float32-arithmetic kernels otherwise
@@ -91,14 +95,26 @@ class GQAttention:
         n = x.shape[0]
         qkv = ctx.buffer("attn.qkv", (n, self.qkv_dim), rt.dtype)
         rt.linear(x, self.qkv, out=qkv)
-        cos = sin = None
-        rotary_dim = 0
-        if self.position is not None:
-            cos, sin, rotary_dim = self.position.tables()
-        ops.qk_norm_rope_append(
-            qkv, n, self.n_heads, self.n_kv_heads, self.head_dim, self.q_norm, self.k_norm, self.eps, cos, sin,
-            rotary_dim, ctx.token_seq, ctx.token_pos, ctx.seq_slot, ctx.seq_qstart, view.page_table, view.num_pages, view.k_pages,
-            view.v_pages, writes_cache, rt.status)
+        where = (ctx.token_seq, ctx.token_pos, ctx.seq_slot, ctx.seq_qstart, view.page_table, view.num_pages,
+                 view.k_pages, view.v_pages)
+        shape = (qkv, n, self.n_heads, self.n_kv_heads, self.head_dim)
+        if self.position is None or self.fused_position:
+            cos = sin = None
+            rotary_dim = 0
+            if self.position is not None:
+                cos, sin, rotary_dim = self.position.tables()
+            ops.qk_norm_rope_append(*shape, self.q_norm, self.k_norm, self.eps, cos, sin, rotary_dim, *where,
+                                    writes_cache, rt.status)
+        else:
+            # in the order of the fused kernel: q/k-norm in place, then the position encoding's own code on
+            # q and k (views of the fused buffer, [N, heads, head_dim]), then the append of k and v
+            if self.q_norm is not None:
+                ops.qk_norm_rope_append(*shape, self.q_norm, self.k_norm, self.eps, None, None, 0, *where, False, rt.status)
+            qd, kd = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+            self.position.apply(qkv[:, :qd].view(n, self.n_heads, self.head_dim),
+                                qkv[:, qd:qd + kd].view(n, self.n_kv_heads, self.head_dim), ctx.token_pos)
+            if writes_cache:
+                ops.qk_norm_rope_append(*shape, None, None, self.eps, None, None, 0, *where, True, rt.status)
         out = ctx.buffer("attn.out", (n, self.n_heads * self.head_dim), rt.dtype)
         self.attend(qkv, out, ctx, view)
         delta = ctx.buffer("attn.delta", (n, self.hidden), rt.dtype)

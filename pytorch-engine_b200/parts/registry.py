@@ -12,8 +12,10 @@ the loader read them, on the run device):
                 ``add_forward(residual_f32, delta, rows=None) -> y``: adds ``delta`` into the
                 float32 residual stream in place (``rows`` given: gathers those rows instead
                 and leaves the stream alone) and returns the normalised rows in the run dtype.
-* position:     ``apply(q, k, positions)`` in place on ``[N, heads, d]`` tensors; a rotary
-                encoding also offers ``tables()`` so that a mixer can fuse it into its own kernel.
+* position:     ``apply(q, k, positions)`` in place on ``[N, heads, d]`` tensors (views of a wider
+                buffer; ``positions`` int32 on the device), or, for a rotary encoding,
+                ``fusable_rotary = True`` and ``tables() -> (cos, sin, rotary_dim)`` so that a mixer
+                fuses it into its own kernel.  The attention mixer takes either.
 * mixer:        ``cache_request(params) -> CacheRequest | None`` (classmethod) and
                 ``forward(x, ctx, cache_view) -> delta`` with ``x`` ``[N, hidden]`` in the run dtype.
 * feed_forward: ``forward(x, ctx) -> delta``.

@@ -42,12 +42,16 @@ def _rows(path, n, vocab):
     return torch.frombuffer(bytearray(open(path, "rb").read()), dtype=torch.float32).view(n, vocab)
 
 
-def run(preset: str, layers=None, lengths=(96, 41), one_by_one: int = 8, seed: int = 0, verbose: bool = True):
-    """{(dtype, way): worst relative error}."""
+def run(preset: str, layers=None, lengths=(96, 41), one_by_one: int = 8, seed: int = 0, verbose: bool = True,
+        **overrides):
+    """{(dtype, way): worst relative error}.  ``overrides`` replace keys of the preset (a smaller vocabulary keeps
+    the plain implementation's time down when the prompt is long)."""
     import pytorch_engine_b200 as pe
     from importlib import import_module
 
-    over = {"num_hidden_layers": int(layers)} if layers else {}
+    over = dict(overrides)
+    if layers:
+        over["num_hidden_layers"] = int(layers)
     cfg = pe.config.preset(preset, **over)
     plan = import_module("pytorch-engine_b200.config.registry").architecture(cfg.architecture).plan(cfg)
     t0 = time.time()
@@ -72,8 +76,8 @@ def run(preset: str, layers=None, lengths=(96, 41), one_by_one: int = 8, seed: i
         else:
             worst[dtype, NOISE] = max(
                 float((a.double() - b.double()).abs().max()) for a, b in zip(refs, exact)) / scale
-        eng = pe.Engine(None, config=cfg, weights=dict(weights), dtype=dtype, max_context_len=256, max_cache_tokens=1024,
-                        max_batch=4)
+        eng = pe.Engine(None, config=cfg, weights=dict(weights), dtype=dtype, max_context_len=max(256, max(lengths) + 64),
+                        max_cache_tokens=max(1024, 4 * (sum(lengths) + 128)), max_batch=4)
         with tempfile.TemporaryDirectory() as out:
             rep = pe.engine.replay.TraceReplayer(eng, out)
             step = [0]
@@ -141,8 +145,10 @@ def main() -> int:
     ap.add_argument("--preset", default="qwen3_0_6b")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the preset has")
     ap.add_argument("--lengths", default="96,41")
+    ap.add_argument("--vocab", type=int, default=None, help="another vocabulary size than the preset's")
     a = ap.parse_args()
-    worst = run(a.preset, a.layers, tuple(int(x) for x in a.lengths.split(",")))
+    worst = run(a.preset, a.layers, tuple(int(x) for x in a.lengths.split(",")),
+                **({"vocab_size": a.vocab} if a.vocab else {}))
     bad = failures(worst)
     print("parity " + ("FAILED: " + str(bad) if bad else "ok"))
     return 1 if bad else 0

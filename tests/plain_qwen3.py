@@ -312,26 +312,56 @@ def filter_logits(
     return logits, probs
 
 
+def gumbel_scores(logits: torch.Tensor, *, seed: int, request: int, step: int, **filters) -> Optional[torch.Tensor]:
+    """``log p_i - log(-log u_i)`` for every kept entry (minus infinity for the dropped ones) with the engine's
+    counter-based uniform numbers, float64; None for a greedy draw."""
+    _, probs = filter_logits(logits, **filters)
+    if probs is None:
+        return None
+    logp = torch.log(probs.to(torch.float64))
+    scores = torch.full_like(logp, -float("inf"))
+    for i in range(probs.numel()):
+        if probs[i] <= 0:
+            continue
+        u = uniform_for(seed, request, step, i)
+        scores[i] = float(logp[i]) - math.log(-math.log(u))
+    return scores
+
+
 def sample_token(logits: torch.Tensor, *, seed: int, request: int, step: int, **filters) -> int:
     """Greedy argmax, or a draw from the filtered distribution by the Gumbel-max rule with the
     engine's counter-based uniform numbers: ``argmax(log p_i - log(-log u_i))`` over kept entries.
     (The reference draws with ``torch.multinomial``, pygguf_engine/engine.py:149; its stream depends
     on the batch layout, so the engine keys its numbers by request and step instead.)
     """
-    pen, probs = filter_logits(logits, **filters)
-    if probs is None:
+    scores = gumbel_scores(logits, seed=seed, request=request, step=step, **filters)
+    if scores is None:
+        pen, _ = filter_logits(logits, **filters)
         return int(torch.argmax(pen))
-    best, best_i = -float("inf"), -1
-    logp = torch.log(probs.to(torch.float64))
-    for i in range(probs.numel()):
-        if probs[i] <= 0:
-            continue
-        u = uniform_for(seed, request, step, i)
-        g = -math.log(-math.log(u))
-        val = float(logp[i]) + g
-        if val > best:
-            best, best_i = val, i
-    return best_i
+    return int(torch.argmax(scores))         # the first of equal scores, as a loop with ">" would keep
+
+
+def check_drawn_tokens(cfg: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int], tokens: Sequence[int], *,
+                       seed: int, request: int, margin: float, **filters) -> int:
+    """Follows ``tokens`` (what an engine drew for ``prompt``) and checks each against this file's own draw
+    from this file's own logits, with the same seed, request number and step.  A token may differ only where
+    the two best scores lie within ``margin`` of each other (the engine's logits differ from these by rounding,
+    so a near tie may fall the other way; its choice must then be the runner-up) .  Returns how many differed."""
+    toks = list(prompt)
+    differed = 0
+    for j, tok in enumerate(tokens):
+        row = forward_logits(cfg, w, toks)[-1]
+        scores = gumbel_scores(row, seed=seed, request=request, step=j, **filters)
+        if scores is None:
+            scores = filter_logits(row, **filters)[0].to(torch.float64)
+        best = torch.topk(scores, 2)
+        if int(best.indices[0]) != tok:
+            assert float(best.values[0] - best.values[1]) < margin and int(best.indices[1]) == tok, (
+                f"request {request}, token {j}: the engine drew {tok}, the plain draw is {int(best.indices[0])} "
+                f"(score {float(best.values[0]):.6f}, runner-up {int(best.indices[1])} at {float(best.values[1]):.6f})")
+            differed += 1
+        toks.append(tok)
+    return differed
 
 
 def generate_greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int], max_tokens: int,

@@ -188,3 +188,35 @@ def test_decode_attention_ranges(pe):
     for slots, pairs, kv in [(296, 7, 5000), (592, 100, 70000), (10, 1000, 64)]:
         sk, n, least = f(slots, pairs, kv, 512)
         assert sk == 0 and 1 <= n <= max(1, -(-kv // 512)) and least in (512, 2048)
+
+
+def test_reset_forgets_everything_and_loses_nothing(pe):
+    c = _cache(pe, window=100, with_state=True)
+    slots = [c.alloc_slot() for _ in range(3)]
+    for s, n in zip(slots, (200, 1, 130)):
+        c.reserve(s, n)
+        c.commit(s, n)
+    c.view(3).state("acc")[slots[1]].fill_(7.0)
+    assert c.free_pages() < 12
+    c.reset()
+    assert c.live_slots == [] and c.free_pages() == 12
+    c.check()
+    again = [c.alloc_slot() for _ in range(4)]            # every slot can be taken again, with its state at zero
+    assert sorted(again) == [0, 1, 2, 3] and float(c.view(3).state("acc").abs().sum()) == 0.0
+    c.reserve(again[0], 512)
+    c.commit(again[0], 512)
+    c.reset()
+    c.reset()                                             # nothing live: nothing to do
+    c.check()
+
+
+def test_entries_of_a_block_with_two_mixers(pe):
+    """A block with several mixers has one cache entry per mixer, keyed (entry, mixer name)."""
+    CR = pe.parts.CacheRequest
+    reqs = {0: CR("kv", kv_heads=2, head_dim=16), (1, "local"): CR("kv", kv_heads=2, head_dim=16, window=64),
+            (1, "global"): CR("kv", kv_heads=2, head_dim=16), (1, "memory"): CR("state", state_shapes=(("m", (4,), "float32"),))}
+    c = pe.cache.PagedCache(reqs, max_tokens=256, max_slots=2, max_seq_len=256, dtype=torch.float32, device="cpu")
+    assert [(g.request.kind, g.request.window, g.entries) for g in c.groups] == [
+        ("kv", None, [0, (1, "global")]), ("kv", 64, [(1, "local")]), ("state", None, [(1, "memory")])]
+    assert c.view((1, "global")).index == 1 and c.view((1, "local")).window == 64
+    assert c.view((1, "memory")).state("m").shape == (2, 4) and c.view((1, "nothing")) is None

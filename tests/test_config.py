@@ -87,3 +87,35 @@ def test_presets_are_config_files(pe):
             c.intermediate_size, c.vocab_size) == (36, 4096, 32, 8, 128, 12288, 151936)
     with pytest.raises(pe.ConfigError):
         pe.preset("nope")
+
+
+def test_a_preset_is_read_by_the_class_its_own_json_names(pe, tmp_path):
+    """Presets go through the registry: a folder of config files is registered, and each file's
+    ``architectures[0]`` picks the class that reads it, so another architecture's sizes need no edit here."""
+    import json
+    from dataclasses import dataclass
+
+    @dataclass(frozen=True)
+    class OtherConfig(pe.config.ModelConfig):
+        width: int = 0
+        architecture: str = "OtherLM"
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(width=int(d["width"]))
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "width": self.width}
+
+    (tmp_path / "other_small.json").write_text(json.dumps({"architectures": ["OtherLM"], "width": 24}))
+    pe.register_architecture("OtherLM", OtherConfig, lambda cfg: None, replace=True)
+    pe.config.register_preset_folder(str(tmp_path))
+    try:
+        assert "other_small" in pe.config.preset_names() and "tiny_a" in pe.config.preset_names()
+        assert pe.preset("other_small") == OtherConfig(width=24)
+        assert pe.preset("other_small", width=7).width == 7
+        assert isinstance(pe.preset("tiny_a"), pe.Qwen3Config)
+    finally:
+        pe.config.unregister_preset_folder(str(tmp_path))
+        pe.config.unregister_architecture("OtherLM")
+    assert "other_small" not in pe.config.preset_names()

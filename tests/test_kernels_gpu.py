@@ -603,6 +603,41 @@ def test_gemm_umma_with_the_gate_fused(ops, M, I, K, kernel):
     assert rel_err(out.float().cpu(), want) < KTOL[torch.bfloat16]
 
 
+@pytest.mark.parametrize("M,N,K,fused", [(2048, 4096, 12288, False), (1536, 6144, 4096, False), (1024, 4096, 4096, False),
+                                         (2048, 12288, 4096, True)])
+@pytest.mark.parametrize("kernel", ["gemm_umma", "gemm_umma2"])
+def test_gemm_umma_at_the_layer_shapes_of_an_8b_model(ops, M, N, K, fused, kernel):
+    """The products of a 2,048-token prompt at width 4,096 / 12,288 (K = 12,288 is 192 k blocks: the 3- and 4-stage
+    rings turn over dozens of times).  Every output against the library's true float32 product on the device, and
+    a sample of rows against a float64 product on the CPU."""
+    torch.manual_seed(33)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    rows_w = 2 * N if fused else N
+    w = (torch.randn(rows_w, K, device=DEV) * (2.0 / K ** 0.5)).to(torch.bfloat16)
+    st = _status()
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16 if fused else torch.float32)
+    getattr(ops, kernel)(x, w, out, st, **({"pair_offset": N} if fused else {}))
+    assert st.tolist()[0] == 0
+
+    def finish(prod):
+        if not fused:
+            return prod
+        g, u = prod[:, :N], prod[:, N:]
+        return g / (1 + torch.exp(-g)) * u
+
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        want = finish(torch.mm(x.float(), w.float().t()))
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    tol = KTOL[torch.bfloat16] if fused else 2e-5
+    assert rel_err(out.float().cpu(), want.cpu()) < tol
+    pick = torch.randperm(M)[:48].sort().values
+    exact = finish(x[pick].double().cpu() @ w.double().cpu().T)
+    assert rel_err(out[pick].double().cpu(), exact) < tol
+
+
 def test_sampler_greedy_and_ties(ops):
     torch.manual_seed(8)
     logits = torch.randn(6, 1000, device=DEV)

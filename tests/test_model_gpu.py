@@ -363,12 +363,14 @@ def test_seeded_sampling_does_not_depend_on_batching(pe, engines, oracles):
     assert [r.token_ids for r in together] == [r.token_ids for r in one_by_one]
     other = engines("B", "float32").generate(prompts, pe.SamplingParams(max_tokens=16, temperature=0.8, seed=12))
     assert [r.token_ids for r in together] != [r.token_ids for r in other]
-    # the draws follow the plain restatement of the filters and the generator
-    r0 = together[0]
-    ref = plain.forward_logits(cfg, w, prompts[0] + r0.token_ids)
-    for j, tok in enumerate(r0.token_ids[:6]):
-        _, probs = plain.filter_logits(ref[len(prompts[0]) - 1 + j], temperature=0.8, top_k=40, top_p=0.95, min_p=0.05)
-        assert probs[tok] > 0
+    # every drawn token is the plain restatement's draw (same filters, same generator, keyed by the request's
+    # number in the call and by how many tokens it has drawn), from the plain implementation's own logits
+    differed = 0
+    for r, res in enumerate(together):
+        assert res.completion_tokens == 16
+        differed += plain.check_drawn_tokens(cfg, w, prompts[r], res.token_ids, seed=11, request=r, margin=1e-3,
+                                             temperature=0.8, top_k=40, top_p=0.95, min_p=0.05)
+    assert differed <= 2          # near ties may fall the other way; they are rare
 
 
 def test_cache_too_small_is_an_error_not_a_wrong_result(pe, engines, oracles):

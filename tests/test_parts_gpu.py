@@ -679,3 +679,191 @@ def test_toy_norm(pe):
     finally:
         pe.parts.unregister("norm", "centered")
         pe.config.unregister_architecture("ToyCenteredLM")
+
+
+# ---- a position encoding without rotary tables, and a block with four norms ----------------------------------
+class LearnedAbsolutePosition:
+    """A learned vector per position, added to every query and key head (nothing rotates).  It has no
+    ``tables()``: attention calls ``apply`` between its q/k-norm and the append to the cache."""
+
+    graph_safe = True   # apply() only launches
+
+    @classmethod
+    def weight_decls(cls, params):
+        from importlib import import_module
+        WeightDecl = import_module("pytorch-engine_b200").parts.WeightDecl
+        return {"table": WeightDecl((int(params["max_positions"]), int(params["head_dim"])))}
+
+    def __init__(self, params, weights, runtime):
+        self.table = runtime.adopt(weights["table"])
+
+    def apply(self, q, k, positions):
+        add = self.table.index_select(0, positions.long())[:, None, :]
+        q.add_(add)
+        k.add_(add)
+
+
+class SandwichBlock:
+    """``h = x + post1(mixer(pre1(x)))``; ``out = h + post2(ffn(pre2(h)))``: four norms, the outputs of mixer and
+    feed-forward normalised before they join the stream (the shape of pygguf_engine/model.py:1035-1041)."""
+
+    graph_safe = True
+
+    def __init__(self, spec, parts, runtime):
+        self.rt, self.p = runtime, parts
+
+    def forward(self, stream, pending, ctx, view, writes_cache=True):
+        normed = ctx.buffer("sandwich.normed", tuple(stream.shape), self.rt.dtype)
+        self.p["pre_mixer"].add_forward(stream, pending, normed)
+        mixed = self.p["post_mixer"].forward(self.p["mixer"].forward(normed, ctx, view))
+        self.p["pre_ffn"].add_forward(stream, mixed, normed)
+        return self.p["post_ffn"].forward(self.p["ffn"].forward(normed, ctx))
+
+
+def test_toy_learned_positions_and_a_block_with_four_norms(pe):
+    """Registered from here, with no change to the package: a position encoding that is no rotary table, used by
+    the package's own attention (with q/k-norm, so the order norm -> position -> append shows), and an
+    arrangement whose block carries six parts, four of them norms."""
+    P, B, R = pe.parts.PartSpec, pe.parts.BlockSpec, pe.parts.RunStep
+    eps, theta = 1e-5, 10000.0
+    cfg = ToyMixConfig(hidden_size=48, vocab_size=97, heads=4, kv_heads=2, head_dim=16, architecture="ToySandwichLM")
+
+    def plan(c):
+        h, d = c.hidden_size, c.head_dim
+        norm = lambda n: P("rmsnorm", {"dim": h, "eps": eps}, {"weight": n})
+        att = lambda i, position: P(
+            "attention", {"hidden": h, "n_heads": c.heads, "n_kv_heads": c.kv_heads, "head_dim": d, "qk_norm": True,
+                          "eps": eps, "scale": None, "window": None, "position": position},
+            {k: f"l{i}.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj", "q_norm", "k_norm")})
+        ffn = lambda i: P("swiglu", {"hidden": h, "intermediate": 2 * h},
+                          {"gate_proj": f"l{i}.g", "up_proj": f"l{i}.u", "down_proj": f"l{i}.d"})
+        sandwich = B("sandwich", {"pre_mixer": ("norm", norm("l0.n1")), "mixer": ("mixer", att(0, "learned")),
+                                  "post_mixer": ("norm", norm("l0.n1b")), "pre_ffn": ("norm", norm("l0.n2")),
+                                  "ffn": ("feed_forward", ffn(0)), "post_ffn": ("norm", norm("l0.n2b"))}, name="sandwich")
+        usual = B.standard("pre_norm", norm("l1.n1"), att(1, "rope"), norm("l1.n2"), ffn(1), name="usual")
+        return pe.parts.ModelPlan(
+            hidden_size=h, vocab_size=c.vocab_size, max_positions=c.max_position_embeddings,
+            embedding=P("token_embedding", {"vocab": c.vocab_size, "hidden": h}, {"weight": "emb"}),
+            blocks=(sandwich, usual), order=(R(0), R(1)), final_norm=norm("fn"),
+            head=P("linear_head", {"vocab": c.vocab_size, "hidden": h}, {"weight": "head"}),
+            positions={"rope": P("rope", {"rotary_dim": d, "theta": theta, "max_positions": c.max_position_embeddings}),
+                       "learned": P("learned_abs", {"head_dim": d, "max_positions": c.max_position_embeddings},
+                                    {"table": "pos.table"})})
+
+    pe.parts.register("position", "learned_abs", LearnedAbsolutePosition, replace=True)
+    pe.parts.register("arrangement", "sandwich", SandwichBlock, replace=True)
+    pe.register_architecture("ToySandwichLM", ToyMixConfig, plan, replace=True)
+    try:
+        eng = pe.Engine.from_random(cfg, seed=21, dtype="float32", max_cache_tokens=256, max_batch=2)
+        assert eng.runner.cuda_graphs                       # every part said graph_safe: decode replays graphs
+        labels = [label for label, _, _ in eng.plan.part_specs()]
+        assert "sandwich post_mixer" in labels and "sandwich post_ffn" in labels
+        w = {k: v.float().cpu() for k, v in pe.weights.random_weights(eng.plan, 21, device=DEV).items()}
+        w["pos.table"] = w["pos.table"] * 25.0             # make the position term matter next to unit-norm heads
+        eng = pe.Engine(None, config=cfg, weights={k: v.to(DEV) for k, v in w.items()}, dtype="float32",
+                        max_cache_tokens=256, max_batch=2)
+        nH, nKV, d = cfg.heads, cfg.kv_heads, cfg.head_dim
+
+        def attention(n, i, position):
+            S = n.shape[0]
+            q = plain.rms_norm((n @ w[f"l{i}.q_proj"].T).view(S, nH, d), w[f"l{i}.q_norm"], eps)
+            k = plain.rms_norm((n @ w[f"l{i}.k_proj"].T).view(S, nKV, d), w[f"l{i}.k_norm"], eps)
+            if position == "learned":
+                q, k = q + w["pos.table"][:S, None, :], k + w["pos.table"][:S, None, :]
+            else:
+                cos, sin = plain.rope_cos_sin(torch.arange(S), d, theta)
+                q, k = plain.rope_rotate_neox(q, cos, sin, d), plain.rope_rotate_neox(k, cos, sin, d)
+            v = (n @ w[f"l{i}.v_proj"].T).view(S, nKV, d)
+            return plain.causal_gqa_attention(q, k, v, d ** -0.5).reshape(S, nH * d) @ w[f"l{i}.o_proj"].T
+
+        def plain_toy(tokens, learned=True):
+            x = w["emb"][tokens]
+            mixed = attention(plain.rms_norm(x, w["l0.n1"], eps), 0, "learned" if learned else "none")
+            x = x + plain.rms_norm(mixed, w["l0.n1b"], eps)
+            f = plain.swiglu(plain.rms_norm(x, w["l0.n2"], eps), w["l0.g"], w["l0.u"], w["l0.d"])
+            x = x + plain.rms_norm(f, w["l0.n2b"], eps)
+            x = x + attention(plain.rms_norm(x, w["l1.n1"], eps), 1, "rope")
+            x = x + plain.swiglu(plain.rms_norm(x, w["l1.n2"], eps), w["l1.g"], w["l1.u"], w["l1.d"])
+            return plain.rms_norm(x, w["fn"], eps) @ w["head"].T
+
+        seqs = [[5, 9, 2, 77, 31, 8, 8, 40, 3, 61], [82, 0, 3, 3, 14, 7]]
+        refs = [plain_toy(s) for s in seqs]
+        # the learned positions change the result by far more than the tolerance: the check below sees them
+        assert rel_err(plain_toy(seqs[0], learned=False), refs[0]) > 1e-2
+        for rnd in range(2):
+            slots = [eng.alloc_slot(), eng.alloc_slot()]
+            got = [[], []]
+            lg = eng.step([pe.StepEntry(slots[0], seqs[0][:6], (0, 5)), pe.StepEntry(slots[1], seqs[1][:2], (1,))])
+            got[0] += [lg[0].cpu(), lg[1].cpu()]; got[1].append(lg[2].cpu())
+            for k in range(4):
+                lg = eng.step([pe.StepEntry(slots[0], [seqs[0][6 + k]], (0,)), pe.StepEntry(slots[1], [seqs[1][2 + k]], (0,))])
+                got[0].append(lg[0].cpu()); got[1].append(lg[1].cpu())
+            for s in slots:
+                eng.free_slot(s)
+            assert rel_err(torch.stack(got[0]), refs[0][[0, 5, 6, 7, 8, 9]]) < 1e-5
+            assert rel_err(torch.stack(got[1]), refs[1][[1, 2, 3, 4, 5]]) < 1e-5
+    finally:
+        pe.parts.unregister("position", "learned_abs")
+        pe.parts.unregister("arrangement", "sandwich")
+        pe.config.unregister_architecture("ToySandwichLM")
+
+
+# ---- a state mixer whose decode step only launches: CUDA graphs must fold each token in once ----------------
+class LaunchOnlySumMixer(DecayingSumMixer):
+    """``DecayingSumMixer`` whose one-token step reads nothing on the host, so that decode steps of a model
+    made of it are replayed from CUDA graphs (prompts still go token by token on the host)."""
+
+    graph_safe = True
+
+    def forward(self, x, ctx, view):
+        if not ctx.decode:
+            return super().forward(x, ctx, view)
+        z = self.rt.linear(x, self.proj).float()
+        state = view.state("acc")
+        slots = ctx.seq_slot.long()
+        new = self.decay * state.index_select(0, slots) + z
+        state.index_copy_(0, slots, new)
+        return new.to(x.dtype)
+
+
+def test_state_mixer_under_cuda_graphs_sees_every_token_once(pe):
+    """The first decode step of each batch size is the one that captures a graph; a mixer with state of fixed
+    size would show a token folded in twice there.  Graph replay and eager steps must agree, step by step,
+    as the batch shrinks 3 -> 2 -> 1 (three captures)."""
+    P, B, R = pe.parts.PartSpec, pe.parts.BlockSpec, pe.parts.RunStep
+
+    def plan(cfg):
+        h = cfg.hidden_size
+        norm = lambda n: P("rmsnorm", {"dim": h, "eps": 1e-6}, {"weight": n})
+        blocks = tuple(B.standard("pre_norm", norm(f"l{i}.n1"), P("launch_only_sum", {"hidden": h, "decay": cfg.decay}, {"proj": f"l{i}.proj"}),
+                                  norm(f"l{i}.n2"), P("swiglu", {"hidden": h, "intermediate": 2 * h},
+                                                      {"gate_proj": f"l{i}.g", "up_proj": f"l{i}.u", "down_proj": f"l{i}.d"}),
+                                  name=f"toy {i}") for i in range(cfg.layers))
+        return pe.parts.ModelPlan(hidden_size=h, vocab_size=cfg.vocab_size, max_positions=cfg.max_position_embeddings,
+                                  embedding=P("token_embedding", {"vocab": cfg.vocab_size, "hidden": h}, {"weight": "emb"}),
+                                  blocks=blocks, order=tuple(R(i) for i in range(cfg.layers)), final_norm=norm("fn"),
+                                  head=P("linear_head", {"vocab": cfg.vocab_size, "hidden": h}, {"weight": "emb"}))
+
+    pe.parts.register("mixer", "launch_only_sum", LaunchOnlySumMixer, replace=True)
+    pe.register_architecture("ToyRunningMeanLM", ToyConfig, plan, replace=True)
+    try:
+        cfg = ToyConfig(hidden_size=48, vocab_size=97, layers=2, decay=0.75)
+        seqs = [[5, 9, 2, 77, 31, 8, 8, 40, 1], [96, 0, 3, 3, 14, 9], [7, 7, 50, 2]]
+        runs = {}
+        for graphs in (True, False):
+            eng = pe.Engine.from_random(cfg, seed=4, dtype="float32", max_cache_tokens=256, max_batch=4,
+                                        enable_cuda_graph=graphs)
+            assert eng.runner.cuda_graphs == graphs
+            slots = [eng.alloc_slot() for _ in seqs]
+            out = [eng.step([pe.StepEntry(s, q[:2], (1,)) for s, q in zip(slots, seqs)]).cpu().clone()]
+            for k in range(2, 9):
+                live = [(s, q) for s, q in zip(slots, seqs) if k < len(q)]
+                out.append(eng.step([pe.StepEntry(s, [q[k]], (0,)) for s, q in live]).cpu().clone())
+            runs[graphs] = out
+            if graphs:
+                assert sorted(eng.runner._graphs) == [1, 2, 3]
+        for a, b in zip(runs[True], runs[False]):
+            assert a.shape == b.shape and rel_err(a, b) < 1e-6
+    finally:
+        pe.parts.unregister("mixer", "launch_only_sum")
+        pe.config.unregister_architecture("ToyRunningMeanLM")

@@ -9,9 +9,16 @@ from parity_at_size import NOISE, run
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("preset,layers", [("qwen3_0_6b", None), ("qwen3_8b", 2)])
-def test_parity_at_a_qwen3_size(preset, layers):
-    worst = run(preset, layers, verbose=False)
+@pytest.mark.parametrize("preset,layers,lengths,extra", [
+    ("qwen3_0_6b", None, (96, 41), {}),
+    ("qwen3_8b", 2, (96, 41), {}),
+    # a prompt of more than 1,024 tokens at the 8B widths: the products run on the tcgen05 pair kernel with
+    # K = 4,096 and 12,288, attention on the tcgen05 prefill kernel (one layer and a small vocabulary keep the
+    # plain implementation on the CPU to some seconds)
+    ("qwen3_8b", 1, (1200, 41), {"vocab_size": 8192}),
+])
+def test_parity_at_a_qwen3_size(preset, layers, lengths, extra):
+    worst = run(preset, layers, lengths=lengths, verbose=False, **extra)
     assert len(worst) == 7
     for (dtype, way), err in worst.items():
         if way == NOISE:

@@ -82,3 +82,45 @@ def test_no_alloc_entry_point_refuses_what_does_not_fit(pe):
     assert rc == too_large
     with pytest.raises(pe.kernels.KernelError, match="scratch"):
         pe.kernels.lib.check(rc, "pe_attention_decode_noalloc")
+
+
+def test_a_sequence_longer_than_its_ranges_sets_the_status_word(pe):
+    """``max_splits`` ranges of ``split_keys`` keys must cover every sequence.  The lengths are on the device, so
+    the kernel checks: a longer sequence sets the status word and is merged over the ranges that exist (no read
+    beyond the scratch).  The same check guards the ordinary entry point and the tensor-core one."""
+    lib = pe.kernels.library()
+    ops = pe.kernels.ops
+    nh, nkv, d, split, max_splits = 8, 2, 64, 256, 2
+    stream = torch.cuda.current_stream().cuda_stream
+    lens = [700, 40]                                     # 700 > 2 * 256
+    for dtype in (torch.float32, torch.bfloat16):
+        ps, q, qstart, past = _case(5, lens, nh, nkv, d, dtype)
+        B = len(lens)
+        # what the first 512 keys alone give: the same call on a sequence cut to 512 keys
+        past_cut = torch.tensor([511, 39], dtype=torch.int32, device=DEV)
+        want = torch.zeros(B, nh * d, device=DEV, dtype=dtype)
+        status = torch.zeros(4, dtype=torch.int32, device=DEV)
+        scratch = torch.zeros(ops.attention_generic_scratch_floats(B, nh, d, max_splits), device=DEV)
+        args = (B, 1, nh, nkv, d, 1 / math.sqrt(d), 0, qstart)
+        tail = (ps.seq_slot, ps.table, ps.num_pages, ps.k_pages, ps.v_pages, scratch, split, max_splits, status)
+        ops.attention_generic(True, q, want, *args, past_cut, *tail)
+        assert status.tolist()[0] == 0
+        kernels = [lambda out: ops.attention_generic(True, q, out, *args, past, *tail)]
+        if dtype == torch.bfloat16:
+            kernels.append(lambda out: ops.attention_mma(True, q, out, *args, past, *tail))
+        kernels.append(lambda out: pe.kernels.lib.check(lib.pe_attention_decode_noalloc(
+            ops.dtype_tag(dtype), q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), B, nh, nkv, d,
+            ctypes.c_float(1 / math.sqrt(d)), 0, qstart.data_ptr(), past.data_ptr(), ps.seq_slot.data_ptr(),
+            ps.table.data_ptr(), ps.table.shape[1], ps.num_pages, ps.k_pages.data_ptr(), ps.v_pages.data_ptr(),
+            split, max_splits, status.data_ptr(), stream), "noalloc"))
+        for run in kernels:
+            status.zero_()
+            got = torch.full_like(want, float("nan"))
+            run(got)
+            torch.cuda.synchronize()
+            assert status.tolist() == [3, 0, 699, 512]
+            assert torch.isfinite(got.float()).all()
+            # the long sequence got the attention over the keys its ranges cover; the short one is untouched
+            for row in (0, 1):
+                err = float((got[row].float() - want[row].float()).abs().max() / want[row].float().abs().max())
+                assert err < (5e-6 if dtype == torch.float32 else 8e-3), (row, err)
