@@ -10,6 +10,7 @@ captured for exactly that number of sequences, with slots and lengths read from 
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -148,9 +149,18 @@ class ModelRunner:
         torch.cuda.synchronize(self.runtime.device)
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
-        with torch.cuda.graph(graph, stream=stream):
-            ops.batch_expand(ctx.seq_qstart, ctx.seq_past, n_seqs, ctx.token_seq, ctx.token_pos)
-            logits = self.model.forward(ctx, self.cache)
+        # No collector run in mid-capture: one that frees what an engine dropped earlier left behind (pinned
+        # buffers, events) makes CUDA calls that a capturing stream forbids, and the capture is lost.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+                ops.batch_expand(ctx.seq_qstart, ctx.seq_past, n_seqs, ctx.token_seq, ctx.token_pos)
+                logits = self.model.forward(ctx, self.cache)
+        finally:
+            if collecting:
+                gc.enable()
         launches = ops.launch_count() - before
         if logits.data_ptr() != eager_logits.data_ptr():
             logits.copy_(eager_logits)
