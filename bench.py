@@ -28,6 +28,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+E2E_MIN_WARMUP = 48    # untimed decode steps between the prompts and the timed steps of the end-to-end figure
+
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -305,27 +307,39 @@ def main():
         out["points"] = pts
 
     if not args.no_e2e:
-        # through the public API: real prompts, host token ids in and out at every step; W untimed
-        # decode steps after the prompts, then K timed ones
+        # through the public API: real prompts, host token ids in and out at every step.  The prompts of a
+        # whole batch are seconds' worth of tensor-core work at the board's power cap, after which the clocks
+        # come back over some tens of decode steps; so the untimed steps before the K timed ones are at least
+        # E2E_MIN_WARMUP (the device-timed figure above never sees a prefill).  Host time stamps of every step
+        # and the SM clock sampled meanwhile are kept, so that what the clocks cost can be read off the line.
         steps_e = max(8, K)
-        plen = ctx - steps_e - W - 1
+        warm_e = max(W, E2E_MIN_WARMUP)
+        plen = ctx - steps_e - warm_e - 1
         prompts = [torch.randint(0, vocab, (plen,), generator=gen).tolist() for _ in range(B)]
-        params = pe.SamplingParams.greedy_params(max_tokens=steps_e + W + 1)
-        t_first = None
-        n_tokens = 0
+        params = pe.SamplingParams.greedy_params(max_tokens=steps_e + warm_e + 1)
         got = [0] * B
+        stamps = []                      # host time at which every request has its k-th token
+        sampler = ClockSampler()
+        sampler.start()
+        t_begin = time.perf_counter()
         for chunk in engine.stream_tokens(prompts, params):
             got[chunk.request] += 1
-            if t_first is None:
-                if min(got) >= W + 1:           # every request has its first token and W decoded ones: from
-                    t_first = time.perf_counter()   # this delivery to the last one lie exactly K steps
-            else:
-                n_tokens += 1
+            if min(got) > len(stamps):
+                stamps.append(time.perf_counter())
         torch.cuda.synchronize()
-        dt = time.perf_counter() - t_first
+        clocks_e = sampler.stop()
+        # stamps[0]: first tokens (end of the prompts); stamps[warm_e]: W untimed steps later; then K timed steps
+        dt = stamps[warm_e + steps_e] - stamps[warm_e]
+        n_tokens = B * steps_e
+        step_ms = [(b - a) * 1e3 for a, b in zip(stamps[:-1], stamps[1:])]
         out["e2e"] = {"value": round(n_tokens / dt, 2), "unit": "tokens/s", "tokens": n_tokens,
                       "h2d_bytes_per_step": (B + 3 * B + 1 + B) * 4 + 2 * B * 4, "d2h_bytes_per_step": B * 4 + 16,
-                      "api": "Engine.stream_tokens, greedy, prompts of %d tokens, %d untimed steps" % (plen, W)}
+                      "ms_per_step": round(dt * 1e3 / steps_e, 4),
+                      "prompt_s": round(stamps[0] - t_begin, 3),
+                      "ms_first_steps_after_prompts": [round(x, 2) for x in step_ms[:4]],
+                      "ms_per_step_untimed": round(sum(step_ms[:warm_e]) / warm_e, 4),
+                      "sm_mhz_median_whole_run": clocks_e.get("sm_mhz"), "clock_reasons": clocks_e.get("reasons"),
+                      "api": "Engine.stream_tokens, greedy, prompts of %d tokens, %d untimed steps, %d timed" % (plen, warm_e, steps_e)}
 
     if not args.no_baseline:
         # the same shape as a plain PyTorch model (library products and attention, eager) on this GPU

@@ -24,6 +24,19 @@
 // S of page j + 2 overwrites the columns of P of page j: warp 4 issues it only after P.V of page j
 // has completed.
 // S of the next page is computed while the softmax of the current one runs.  All waits are bounded.
+//
+// Blocks are persistent: the grid is two blocks per SM (or fewer, if there is less work), and each block
+// takes several work items, an item being the 128 rows of one (row tile, sequence, kv head).  Items are
+// ranked with the late row tiles first (under the causal mask they see the most pages).  With a work
+// counter (two ints in global memory, zero before the launch and zero again after it) a block takes the
+// next rank whenever it is free, so the light items at the end even out what the heavy ones left uneven;
+// without one, ranks are dealt out in a serpentine (block c takes ranks c, 2G-1-c, 2G+c, ... of a grid
+// of G blocks).  One 2,048-token prompt with 8 kv heads is 512 items of 1 to 32 pages: a launch of 512
+// blocks in 1.73 waves on 296 slots left the SMs half empty for the second wave.  Which block computes an
+// item changes nothing in its result (the counter only hands out ranks; no sum depends on it).  The
+// producer warp fetches the rank and hands it to the other warps through a two-slot ring in shared memory.
+// Barrier phases, the K/V rings and tensor memory carry over from item to item: every role counts items
+// and pages the same way.
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -47,7 +60,52 @@ struct Args {
   const int* seq_qstart; const int* seq_past; const int* seq_slot;
   const int* page_table; int table_stride; int num_pages;
   int* status;
+  int tiles, n_seqs;      // row tiles of the step's longest sequence; sequences
+  int* work_counter;      // [0] next rank, [1] blocks that are through; both zero between launches.  May be null.
 };
+
+// One work item: the rows [row0, row0 + rows_blk) of sequence b's (token, head) rows for kv head kvh.
+struct Item {
+  int b, kvh, row0, n_rows, q0, past, slot, tok0, k_begin, n_tiles;
+};
+// Rank -> item (late row tiles first, then sequences, then kv heads); false if the sequence has no such rows.
+__device__ __forceinline__ bool item_at(const Args& a, int rank, int rows_blk, Item& w) {
+  w.kvh = rank % a.n_kv_heads;
+  const int r2 = rank / a.n_kv_heads;
+  w.b = r2 % a.n_seqs;
+  const int tile = a.tiles - 1 - r2 / a.n_seqs;
+  w.q0 = a.seq_qstart[w.b];
+  const int q_len = a.seq_qstart[w.b + 1] - w.q0;
+  w.past = a.seq_past[w.b];
+  w.n_rows = q_len * a.group;
+  w.row0 = tile * rows_blk;
+  if (w.row0 >= w.n_rows) return false;
+  w.slot = a.seq_slot[w.b];
+  w.tok0 = w.row0 / a.group;
+  const int last_row = min(w.n_rows, w.row0 + rows_blk) - 1;
+  const int first_pos = w.past + w.tok0, last_pos = w.past + last_row / a.group;
+  w.k_begin = 0;
+  if (a.window > 0) w.k_begin = max(0, first_pos - a.window + 1) / BN * BN;
+  w.n_tiles = (last_pos + 1 - w.k_begin + BN - 1) / BN;
+  return true;
+}
+// Every block calls this once, when it takes no more ranks: the last of the G blocks through leaves the work
+// counter as it found it, zero (also on the error paths, or the next launch would find no work).
+__device__ __forceinline__ void leave_work_counter(int* counter, int G) {
+  if (counter == nullptr) return;
+  __threadfence();
+  if (atomicAdd(counter + 1, 1) == G - 1) {
+    counter[0] = 0;
+    counter[1] = 0;
+    __threadfence();
+  }
+}
+// The rank that block c of G takes in pass p (serpentine), or -1 when the passes are over.
+__device__ __forceinline__ int rank_of(int pass, int c, int G, int total) {
+  if (pass * G >= total) return -1;
+  const int rank = (pass & 1) ? (pass + 1) * G - 1 - c : pass * G + c;
+  return rank < total ? rank : total;      // total: nothing for this block in this pass
+}
 
 // ---- tcgen05 wrappers (see gemm_umma.cu for the descriptor layouts) ------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t cols) {
@@ -134,15 +192,13 @@ __device__ __forceinline__ void load_3d(void* dst, const CUtensorMap* map, int x
       ::"r"(tma::smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(tma::smem_addr(bar)) : "memory");
 }
 
-// grid: (row tiles of 128, n_kv_heads, n_seqs), late row tiles first; block: 192 threads.
+// grid: G persistent blocks (see the file's head); block: 192 threads.
 __global__ void __launch_bounds__(192, 2)
 prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                     const __grid_constant__ CUtensorMap vmap) {
   // All shared memory is dynamic and starts on a 1,024-byte boundary (there are no static shared
   // variables in front of it), so that two blocks fit on an SM: tiles first, barriers behind them.
   extern __shared__ __align__(1024) char smem[];
-  pdl_wait_block();
-  pdl_launch_dependents();
   char* q_s = smem;                       // [2 halves][128 rows][128 B]
   char* k_s = q_s + kQBytes;              // kKStages K pages
   char* v_s = k_s + kKStages * kPageBytes;   // kVStages V pages
@@ -155,31 +211,28 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
   uint64_t* s_full = bars + 11;   // [2]
   uint64_t* p_ready = bars + 13;  // [2]: one per S buffer, the softmax may be a page ahead of the P.V products
   uint64_t& pv_done = bars[15];   // one phase per page: waited for only before O is rescaled
-  uint64_t& o_done = bars[16];    // the last P.V product is done.  (A barrier of its own: the softmax does not
-                                  // follow pv_done phase by phase, and a parity wait that is two phases
-                                  // ahead of the barrier passes at once.)
-  uint32_t& tmem_holder = *reinterpret_cast<uint32_t*>(bars + 17);
-  volatile int& failed = *reinterpret_cast<volatile int*>(bars + 18);
+  uint64_t& o_done = bars[16];    // one phase per item: its last P.V product is done.  (A barrier of its own: the
+                                  // softmax does not follow pv_done phase by phase, and a parity wait that is two
+                                  // phases ahead of the barrier passes at once.)
+  uint64_t& q_empty = bars[17];   // one phase per item: its last S product has read Q
+  uint64_t& o_free = bars[18];    // one phase per item: the softmax threads have read O out
+  uint64_t* w_full = bars + 19;   // [2]: a rank has been put into the slot
+  uint64_t* w_empty = bars + 21;  // [2]: the MMA thread and the 128 softmax threads have read it
+  uint32_t& tmem_holder = *reinterpret_cast<uint32_t*>(bars + 23);
+  volatile int& failed = *reinterpret_cast<volatile int*>(bars + 24);
+  volatile int* work_slot = reinterpret_cast<volatile int*>(bars + 25);   // [2] ranks; -1: no more work
   if ((tma::smem_addr(smem) & 1023u) != 0) {   // the swizzled tiles need this alignment
-    if (threadIdx.x == 0) report(a.status, kStatusWaitTimedOut, 29, (int)(tma::smem_addr(smem) & 1023u), 0);
+    if (threadIdx.x == 0) {
+      report(a.status, kStatusWaitTimedOut, 29, (int)(tma::smem_addr(smem) & 1023u), 0);
+      leave_work_counter(a.work_counter, (int)gridDim.x);
+    }
     return;
   }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int b = blockIdx.z, kvh = blockIdx.y;
   const int group = a.group;
-  const int q0 = a.seq_qstart[b], q_len = a.seq_qstart[b + 1] - q0, past = a.seq_past[b];
-  const int n_rows = q_len * group;
   const int rows_blk = (BM / group) * group;                  // whole tokens only
-  const int row0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * rows_blk;
-  if (row0 >= n_rows) return;
-  const int slot = a.seq_slot[b];
-  const int tok0 = row0 / group;
-  const int last_row = min(n_rows, row0 + rows_blk) - 1;
-  const int first_pos = past + tok0, last_pos = past + last_row / group;
-  int k_begin = 0;
-  if (a.window > 0) k_begin = max(0, first_pos - a.window + 1) / BN * BN;
-  const int k_end = last_pos + 1;
-  const int n_tiles = (k_end - k_begin + BN - 1) / BN;
+  const int G = (int)gridDim.x, me = (int)blockIdx.x;
+  const int total = a.tiles * a.n_seqs * a.n_kv_heads;
 
   if (tid == 0) {
     tma::mbar_init(&q_full, 1);
@@ -195,6 +248,12 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
     }
     tma::mbar_init(&pv_done, 1);
     tma::mbar_init(&o_done, 1);
+    tma::mbar_init(&q_empty, 1);
+    tma::mbar_init(&o_free, 128);
+    for (int s = 0; s < 2; ++s) {
+      tma::mbar_init(&w_full[s], 1);
+      tma::mbar_init(&w_empty[s], 129);
+    }
     failed = 0;
     tma::fence_barrier_init();
   }
@@ -207,46 +266,82 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
   tma::fence_proxy_async();
   if (warp == 4) tmem_alloc(&tmem_holder, kTmemCols);
   fence_before_sync();
-  __syncthreads();
+  // Barriers, the zeroed Q rows and tensor memory touch nothing that another kernel of the step writes: all of
+  // that is done while the kernel before may still be draining; only now wait for it (its output is q, K, V).
+  pdl_wait_block();
+  pdl_launch_dependents();
   fence_after_sync();
   const uint32_t tmem_base = tmem_holder;
   const uint32_t tmem_o = tmem_base + 128;
 
+  // Every role walks the same items in the same order and counts alike: `it` items done, `n` pages done.
+  uint32_t it = 0, n = 0;
   if (warp == 5) {
     // ---- TMA producer ----
     if (lane == 0) {
-      tma::mbar_expect_tx(&q_full, (uint32_t)(rows_blk * HD * 2));
-      load_3d(q_s, &qmap, 0, kvh * group, q0 + tok0, &q_full);
-      load_3d(q_s + kQBytes / 2, &qmap, 64, kvh * group, q0 + tok0, &q_full);
-      for (int j = 0; j < n_tiles && !failed; ++j) {
-        const int k0 = k_begin + j * BN;
-        const int logical = k0 / BN;
-        int page = -1;
-        if (logical < a.table_stride) page = a.page_table[(size_t)slot * a.table_stride + logical];
-        if (page < 0 || page >= a.num_pages) {
-          report(a.status, kStatusPageOutOfRange, slot, page, k0);
-          page = 0;
+      for (uint32_t f = 0;; ++f) {
+        // the next rank: from the counter, or by the serpentine; into the ring for the other warps
+        int rank = -1;
+        if (!failed) {
+          if (a.work_counter != nullptr) {
+            rank = atomicAdd(a.work_counter, 1);
+            if (rank >= total) rank = -1;
+          } else {
+            rank = rank_of((int)f, me, G, total);
+          }
+          if (f >= 2 && !tma::mbar_wait(&w_empty[f & 1], ((f >> 1) & 1) ^ 1)) {
+            report(a.status, kStatusWaitTimedOut, 26, me, (int)f);
+            failed = 1;
+            rank = -1;
+          }
         }
-        const int y = (page * a.n_kv_heads + kvh) * BN;
-        const int ks = j % kKStages, vs = j % kVStages;
-        if (!tma::mbar_wait(&k_empty[ks], ((j / kKStages) & 1) ^ 1)) {
-          report(a.status, kStatusWaitTimedOut, 20, blockIdx.x, j);
+        work_slot[f & 1] = rank;
+        tma::mbar_arrive(&w_full[f & 1]);
+        if (rank < 0) break;
+        Item w;
+        if (rank >= total || !item_at(a, rank, rows_blk, w)) continue;
+        // Q of the item before must have been read by its last S product
+        if (!tma::mbar_wait(&q_empty, (it & 1) ^ 1)) {
+          report(a.status, kStatusWaitTimedOut, 25, me, (int)it);
           failed = 1;
-          break;
+          continue;              // the loop's head then tells the other warps that nothing follows
         }
-        char* kd = k_s + ks * kPageBytes;
-        tma::mbar_expect_tx(&k_full[ks], kPageBytes);
-        tma::load_2d(kd, &kmap, 0, y, &k_full[ks]);
-        tma::load_2d(kd + BN * 128, &kmap, 64, y, &k_full[ks]);
-        if (!tma::mbar_wait(&v_empty[vs], ((j / kVStages) & 1) ^ 1)) {
-          report(a.status, kStatusWaitTimedOut, 24, blockIdx.x, j);
-          failed = 1;
-          break;
+        tma::mbar_expect_tx(&q_full, (uint32_t)(rows_blk * HD * 2));
+        load_3d(q_s, &qmap, 0, w.kvh * group, w.q0 + w.tok0, &q_full);
+        load_3d(q_s + kQBytes / 2, &qmap, 64, w.kvh * group, w.q0 + w.tok0, &q_full);
+        for (int j = 0; j < w.n_tiles && !failed; ++j) {
+          const uint32_t g = n + j;
+          const int k0 = w.k_begin + j * BN;
+          const int logical = k0 / BN;
+          int page = -1;
+          if (logical < a.table_stride) page = a.page_table[(size_t)w.slot * a.table_stride + logical];
+          if (page < 0 || page >= a.num_pages) {
+            report(a.status, kStatusPageOutOfRange, w.slot, page, k0);
+            page = 0;
+          }
+          const int y = (page * a.n_kv_heads + w.kvh) * BN;
+          const int ks = g % kKStages, vs = g % kVStages;
+          if (!tma::mbar_wait(&k_empty[ks], ((g / kKStages) & 1) ^ 1)) {
+            report(a.status, kStatusWaitTimedOut, 20, me, j);
+            failed = 1;
+            break;
+          }
+          char* kd = k_s + ks * kPageBytes;
+          tma::mbar_expect_tx(&k_full[ks], kPageBytes);
+          tma::load_2d(kd, &kmap, 0, y, &k_full[ks]);
+          tma::load_2d(kd + BN * 128, &kmap, 64, y, &k_full[ks]);
+          if (!tma::mbar_wait(&v_empty[vs], ((g / kVStages) & 1) ^ 1)) {
+            report(a.status, kStatusWaitTimedOut, 24, me, j);
+            failed = 1;
+            break;
+          }
+          char* vd = v_s + vs * kPageBytes;
+          tma::mbar_expect_tx(&v_full[vs], kPageBytes);
+          tma::load_2d(vd, &vmap, 0, y, &v_full[vs]);
+          tma::load_2d(vd + BN * 128, &vmap, 64, y, &v_full[vs]);
         }
-        char* vd = v_s + vs * kPageBytes;
-        tma::mbar_expect_tx(&v_full[vs], kPageBytes);
-        tma::load_2d(vd, &vmap, 0, y, &v_full[vs]);
-        tma::load_2d(vd + BN * 128, &vmap, 64, y, &v_full[vs]);
+        n += w.n_tiles;
+        ++it;
       }
     }
   } else if (warp == 4) {
@@ -255,166 +350,208 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       const uint32_t idesc_qk = instr_desc(BM, BN, false);
       const uint32_t idesc_pv = instr_desc(BM, HD, true);
       const uint32_t q_addr = tma::smem_addr(q_s);
-      auto issue_qk = [&](int j) -> bool {
-        const int st = j & 1, ks = j % kKStages;
-        if (!tma::mbar_wait(&k_full[ks], (j / kKStages) & 1)) return false;
-        fence_after_sync();
-        const uint32_t k_addr = tma::smem_addr(k_s + ks * kPageBytes);
+      bool ok = true;
+      for (uint32_t f = 0; ok && !failed; ++f) {
+        if (!tma::mbar_wait(&w_full[f & 1], (f >> 1) & 1)) { ok = false; break; }
+        const int rank = work_slot[f & 1];
+        tma::mbar_arrive(&w_empty[f & 1]);
+        if (rank < 0) break;
+        Item w;
+        if (rank >= total || !item_at(a, rank, rows_blk, w)) continue;
+        const int n_tiles = w.n_tiles;
+        auto issue_qk = [&](int j) -> bool {
+          const uint32_t g = n + j;
+          const int st = g & 1, ks = g % kKStages;
+          if (!tma::mbar_wait(&k_full[ks], (g / kKStages) & 1)) return false;
+          fence_after_sync();
+          const uint32_t k_addr = tma::smem_addr(k_s + ks * kPageBytes);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t off_a = (k >> 2) * (BM * 128) + (k & 3) * 32;
-          const uint32_t off_b = (k >> 2) * (BN * 128) + (k & 3) * 32;
-          umma_bf16(tmem_base + st * BN, desc_k_major(q_addr + off_a), desc_k_major(k_addr + off_b), idesc_qk, k > 0 ? 1u : 0u);
+          for (int k = 0; k < HD / 16; ++k) {
+            const uint32_t off_a = (k >> 2) * (BM * 128) + (k & 3) * 32;
+            const uint32_t off_b = (k >> 2) * (BN * 128) + (k & 3) * 32;
+            umma_bf16(tmem_base + st * BN, desc_k_major(q_addr + off_a), desc_k_major(k_addr + off_b), idesc_qk, k > 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[st]);     // S is there ...
+          umma_commit(&k_empty[ks]);    // ... and the K page is spent
+          if (j == n_tiles - 1) umma_commit(&q_empty);   // ... and so is Q, after the item's last S product
+          return true;
+        };
+        ok = tma::mbar_wait(&q_full, it & 1);
+        if (ok) ok = issue_qk(0);
+        for (int j = 0; ok && j < n_tiles; ++j) {
+          const uint32_t g = n + j;
+          // S of page j + 1 goes where P of page j - 1 lies: that P.V product must have read it.  (Products
+          // of one thread run in issue order on today's hardware; the wait makes the order explicit and
+          // costs nothing, the softmax of page j is still running.)  Across items nothing is pending: an
+          // item ends with all its products complete.
+          if (j >= 1 && j + 1 < n_tiles && !tma::mbar_wait(&pv_done, (g - 1) & 1)) { ok = false; break; }
+          if (j + 1 < n_tiles) ok = issue_qk(j + 1);        // S of the next page while this one's softmax runs
+          if (!ok) break;
+          const int st = g & 1, vs = g % kVStages;
+          if (!tma::mbar_wait(&p_ready[st], (g >> 1) & 1)) { ok = false; break; }
+          if (!tma::mbar_wait(&v_full[vs], (g / kVStages) & 1)) { ok = false; break; }
+          // the first product of an item starts O anew: the item before must have been read out of it
+          if (j == 0 && !tma::mbar_wait(&o_free, (it & 1) ^ 1)) { ok = false; break; }
+          fence_after_sync();
+          const uint32_t p_tmem = tmem_base + st * BN;       // P lies where S of this page was (bfloat16 pairs, 32 columns)
+          const uint32_t v_addr = tma::smem_addr(v_s + vs * kPageBytes);
+#pragma unroll
+          for (int k = 0; k < BN / 16; ++k)
+            umma_bf16_a_tmem(tmem_o, p_tmem + k * 8, desc_mn_major(v_addr + k * 16 * 128, BN * 128), idesc_pv,
+                             (j > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&v_empty[vs]);
+          umma_commit(&pv_done);
         }
-        umma_commit(&s_full[st]);     // S is there ...
-        umma_commit(&k_empty[ks]);    // ... and the K page is spent
-        return true;
-      };
-      bool ok = tma::mbar_wait(&q_full, 0);
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        // S of page j + 1 goes where P of page j - 1 lies: that P.V product must have read it.  (Products
-        // of one thread run in issue order on today's hardware; the wait makes the order explicit and
-        // costs nothing, the softmax of page j is still running.)
-        if (j >= 1 && j + 1 < n_tiles && !tma::mbar_wait(&pv_done, (j - 1) & 1)) { ok = false; break; }
-        if (j + 1 < n_tiles) ok = issue_qk(j + 1);        // S of the next page while this one's softmax runs
-        if (!ok) break;
-        const int st = j & 1, vs = j % kVStages;
-        if (!tma::mbar_wait(&p_ready[st], (j >> 1) & 1)) { ok = false; break; }
-        if (!tma::mbar_wait(&v_full[vs], (j / kVStages) & 1)) { ok = false; break; }
-        fence_after_sync();
-        const uint32_t p_tmem = tmem_base + st * BN;       // P lies where S of this page was (bfloat16 pairs, 32 columns)
-        const uint32_t v_addr = tma::smem_addr(v_s + vs * kPageBytes);
-#pragma unroll
-        for (int k = 0; k < BN / 16; ++k)
-          umma_bf16_a_tmem(tmem_o, p_tmem + k * 8, desc_mn_major(v_addr + k * 16 * 128, BN * 128), idesc_pv,
-                           (j > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&v_empty[vs]);
-        umma_commit(&pv_done);
+        if (ok) {
+          umma_commit(&o_done);
+          // the item ends with every product complete: the next item's S products overwrite the P columns
+          ok = tma::mbar_wait(&o_done, it & 1);
+        }
+        n += n_tiles;
+        ++it;
       }
-      if (ok) umma_commit(&o_done);
       if (!ok) {
-        report(a.status, kStatusWaitTimedOut, 21, blockIdx.x, blockIdx.y);
+        report(a.status, kStatusWaitTimedOut, 21, me, (int)it);
         failed = 1;
       }
     }
   } else {
     // ---- softmax: thread r owns row r ----
     const int r = tid;                               // 0..127; warp w reads TMEM lanes 32w..32w+31
-    const int row = row0 + r;
-    const bool live = r < rows_blk && row < n_rows;
-    const int qpos = past + row / group;
     const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-    float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int st = j & 1;
-      const int k0 = k_begin + j * BN;
-      if (failed || !tma::mbar_wait(&s_full[st], (j >> 1) & 1)) { ok = false; break; }
-      fence_after_sync();
-      uint32_t sv[2][32];
-      tmem_ld32(tmem_base + st * BN + lane_off, sv[0]);
-      tmem_ld32(tmem_base + st * BN + 32 + lane_off, sv[1]);
-      tmem_ld_wait();
-      // A page that every row of this block sees whole (below the diagonal, inside the window) needs
-      // no mask: the scores stay raw and the scale is folded into the exponent's multiply-add.
-      const bool whole = a.scale_log2 > 0.f && (row0 + rows_blk <= n_rows) && (k0 + BN - 1 <= past + row0 / group) &&
-                         (a.window <= 0 || k0 > past + (row0 + rows_blk - 1) / group - a.window);
-      float mx = -INFINITY;
-      if (whole) {
-        // four independent chains: a thread has few other warps to hide a 64-long dependent chain behind
-        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(sv[h][c]));
-        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * a.scale_log2;   // the scale is positive
-      } else {
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const int kpos = k0 + h * 32 + c;
-            bool vis = live && kpos <= qpos;
-            if (a.window > 0) vis = vis && (kpos > qpos - a.window);
-            const float v = vis ? __uint_as_float(sv[h][c]) * a.scale_log2 : -INFINITY;
-            sv[h][c] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
-          }
+    for (uint32_t f = 0; ok && !failed; ++f) {
+      if (!tma::mbar_wait(&w_full[f & 1], (f >> 1) & 1)) {
+        if (lane == 0) report(a.status, kStatusWaitTimedOut, 27, me, (int)f);
+        failed = 1;
+        break;
       }
-      // move the reference of the exponentials only when the maximum has grown a lot
-      const bool grow = mx > m_ref + kRescaleThreshold;
-      if (__any_sync(0xffffffffu, grow && j > 0 && m_ref != -INFINITY)) {
-        // O is rescaled in place: the previous P.V must be done with it first
-        if (!tma::mbar_wait(&pv_done, (j - 1) & 1)) { ok = false; break; }
+      const int rank = work_slot[f & 1];
+      tma::mbar_arrive(&w_empty[f & 1]);
+      if (rank < 0) break;
+      Item w;
+      if (rank >= total || !item_at(a, rank, rows_blk, w)) continue;
+      const int row0 = w.row0, n_rows = w.n_rows, past = w.past, n_tiles = w.n_tiles;
+      const int row = row0 + r;
+      const bool live = r < rows_blk && row < n_rows;
+      const int qpos = past + row / group;
+      float m_ref = -INFINITY, l = 0.f;
+      for (int j = 0; j < n_tiles; ++j) {
+        const uint32_t g = n + j;
+        const int st = g & 1;
+        const int k0 = w.k_begin + j * BN;
+        if (failed || !tma::mbar_wait(&s_full[st], (g >> 1) & 1)) { ok = false; break; }
         fence_after_sync();
-        const float f = (grow && m_ref != -INFINITY) ? fast_exp2(m_ref - mx) : 1.0f;
+        uint32_t sv[2][32];
+        tmem_ld32(tmem_base + st * BN + lane_off, sv[0]);
+        tmem_ld32(tmem_base + st * BN + 32 + lane_off, sv[1]);
+        tmem_ld_wait();
+        // A page that every row of this block sees whole (below the diagonal, inside the window) needs
+        // no mask: the scores stay raw and the scale is folded into the exponent's multiply-add.
+        const bool whole = a.scale_log2 > 0.f && (row0 + rows_blk <= n_rows) && (k0 + BN - 1 <= past + row0 / group) &&
+                           (a.window <= 0 || k0 > past + (row0 + rows_blk - 1) / group - a.window);
+        float mx = -INFINITY;
+        if (whole) {
+          // four independent chains: a thread has few other warps to hide a 64-long dependent chain behind
+          float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(sv[h][c]));
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * a.scale_log2;   // the scale is positive
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const int kpos = k0 + h * 32 + c;
+              bool vis = live && kpos <= qpos;
+              if (a.window > 0) vis = vis && (kpos > qpos - a.window);
+              const float v = vis ? __uint_as_float(sv[h][c]) * a.scale_log2 : -INFINITY;
+              sv[h][c] = __float_as_uint(v);
+              mx = fmaxf(mx, v);
+            }
+        }
+        // move the reference of the exponentials only when the maximum has grown a lot
+        const bool grow = mx > m_ref + kRescaleThreshold;
+        if (__any_sync(0xffffffffu, grow && j > 0 && m_ref != -INFINITY)) {
+          // O is rescaled in place: the previous P.V must be done with it first
+          if (!tma::mbar_wait(&pv_done, (g - 1) & 1)) { ok = false; break; }
+          fence_after_sync();
+          const float f = (grow && m_ref != -INFINITY) ? fast_exp2(m_ref - mx) : 1.0f;
+#pragma unroll 1
+          for (int c = 0; c < HD; c += 32) {
+            uint32_t ov[32];
+            tmem_ld32(tmem_o + c + lane_off, ov);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
+            tmem_st32(tmem_o + c + lane_off, ov);
+          }
+          tmem_st_wait();
+          l *= f;
+        }
+        if (grow) m_ref = mx;
+        const float base = (m_ref == -INFINITY) ? 0.f : m_ref;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};   // four chains (see the maximum); summed in a fixed order below
+        // P = exp2(score - reference) as bfloat16 pairs, back into tensor memory where S of this page was
+        // (this thread has read all of its S row): the P.V product takes its A operand from there
+        uint32_t pw[32];
+        auto exps = [&](auto exponent) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const float p0 = fast_exp2(exponent(__uint_as_float(sv[h][2 * c])));
+              const float p1 = fast_exp2(exponent(__uint_as_float(sv[h][2 * c + 1])));
+              sum4[c & 3] += p0 + p1;
+              pw[h * 16 + c] = pack2(p0, p1);
+            }
+        };
+        if (whole) {
+          const float sc = a.scale_log2, nb = -base;
+          exps([sc, nb](float s) { return fmaf(s, sc, nb); });
+        } else {
+          exps([base](float s) { return s - base; });
+        }
+        tmem_st32(tmem_base + st * BN + lane_off, pw);
+        tmem_st_wait();
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        fence_before_sync();
+        tma::mbar_arrive(&p_ready[st]);
+      }
+      if (ok && tma::mbar_wait(&o_done, it & 1)) {
+        fence_after_sync();
+        const float inv = 1.f / fmaxf(l, 1e-20f);
+        const int tok = row / group, head = w.kvh * group + row % group;
+        __nv_bfloat16* dst = a.out + (size_t)(w.q0 + tok) * a.out_ld + (size_t)head * HD;
 #pragma unroll 1
         for (int c = 0; c < HD; c += 32) {
           uint32_t ov[32];
           tmem_ld32(tmem_o + c + lane_off, ov);
           tmem_ld_wait();
+          if (live) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
-          tmem_st32(tmem_o + c + lane_off, ov);
-        }
-        tmem_st_wait();
-        l *= f;
-      }
-      if (grow) m_ref = mx;
-      const float base = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};   // four chains (see the maximum); summed in a fixed order below
-      // P = exp2(score - reference) as bfloat16 pairs, back into tensor memory where S of this page was
-      // (this thread has read all of its S row): the P.V product takes its A operand from there
-      uint32_t pw[32];
-      auto exps = [&](auto exponent) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const float p0 = fast_exp2(exponent(__uint_as_float(sv[h][2 * c])));
-            const float p1 = fast_exp2(exponent(__uint_as_float(sv[h][2 * c + 1])));
-            sum4[c & 3] += p0 + p1;
-            pw[h * 16 + c] = pack2(p0, p1);
+            for (int i = 0; i < 4; ++i) {
+              uint4 o4;
+              o4.x = pack2(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
+              o4.y = pack2(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
+              o4.z = pack2(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
+              o4.w = pack2(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c + 8 * i) = o4;
+            }
           }
-      };
-      if (whole) {
-        const float sc = a.scale_log2, nb = -base;
-        exps([sc, nb](float s) { return fmaf(s, sc, nb); });
+        }
+        // O has been read out: the next item's first P.V product may start it anew
+        fence_before_sync();
+        tma::mbar_arrive(&o_free);
       } else {
-        exps([base](float s) { return s - base; });
+        if (lane == 0 && !failed) report(a.status, kStatusWaitTimedOut, 22, me, (int)it);
+        failed = 1;
+        ok = false;
       }
-      tmem_st32(tmem_base + st * BN + lane_off, pw);
-      tmem_st_wait();
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      fence_before_sync();
-      tma::mbar_arrive(&p_ready[st]);
-    }
-    if (ok && tma::mbar_wait(&o_done, 0)) {
-      fence_after_sync();
-      const float inv = 1.f / fmaxf(l, 1e-20f);
-      const int tok = row / group, head = kvh * group + row % group;
-      __nv_bfloat16* dst = a.out + (size_t)(q0 + tok) * a.out_ld + (size_t)head * HD;
-#pragma unroll 1
-      for (int c = 0; c < HD; c += 32) {
-        uint32_t ov[32];
-        tmem_ld32(tmem_o + c + lane_off, ov);
-        tmem_ld_wait();
-        if (live) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 o4;
-            o4.x = pack2(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
-            o4.y = pack2(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
-            o4.z = pack2(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
-            o4.w = pack2(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c + 8 * i) = o4;
-          }
-        }
-      }
-    } else {
-      if (lane == 0 && !failed) report(a.status, kStatusWaitTimedOut, 22, blockIdx.x, blockIdx.y);
-      failed = 1;
+      n += n_tiles;
+      ++it;
     }
   }
   fence_before_sync();
@@ -423,6 +560,7 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
     fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (tid == 0) leave_work_counter(a.work_counter, G);
 }
 
 }  // namespace fau
@@ -435,11 +573,13 @@ extern "C" int pe_attention_umma_supported(int head_dim, int n_heads, int n_kv_h
 }
 
 // Prefill form only (decode keeps attention_mma.cu).  q: rows of the fused q|k|v buffer, [n_tokens, q_ld].
+// n_sms: the device's SM count (sizes the persistent grid).  work_counter: two ints, zero before the call (the
+// kernel leaves them zero), not shared with a call that may run at the same time; null: a fixed schedule.
 extern "C" int pe_attention_umma_prefill(const void* q, long long q_ld, long long n_tokens, void* out, long long out_ld,
                                          int n_seqs, int max_q, int n_heads, int n_kv_heads, int head_dim, float scale,
                                          int window, const int* seq_qstart, const int* seq_past, const int* seq_slot,
                                          const int* page_table, int table_stride, int num_pages, const void* k_pages,
-                                         const void* v_pages, int* status, cudaStream_t stream) {
+                                         const void* v_pages, int n_sms, int* work_counter, int* status, cudaStream_t stream) {
   using namespace pe::fau;
   if (n_seqs <= 0) return PE_OK;
   if (!pe_attention_umma_supported(head_dim, n_heads, n_kv_heads)) return PE_ERR_UNSUPPORTED_SIZE;
@@ -466,7 +606,7 @@ extern "C" int pe_attention_umma_prefill(const void* q, long long q_ld, long lon
   int me = pe::tma::make_map_2d_bf16(&kmap, k_pages, HD, rows, HD, 64, BN);
   if (me == 0) me = pe::tma::make_map_2d_bf16(&vmap, v_pages, HD, rows, HD, 64, BN);
   if (me != 0) return me < 0 ? me : PE_ERR_BAD_ARGUMENT;
-  const size_t smem = kQBytes + (kKStages + kVStages) * kPageBytes + 256;
+  const size_t smem = kQBytes + (kKStages + kVStages) * kPageBytes + 256;   // tiles, then barriers and the two-slot ring
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t ce = cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -475,8 +615,12 @@ extern "C" int pe_attention_umma_prefill(const void* q, long long q_ld, long lon
   }
   const int rows_blk = (BM / a.group) * a.group;
   const long long tiles = ((long long)max_q * a.group + rows_blk - 1) / rows_blk;
-  dim3 grid((unsigned)tiles, n_kv_heads, n_seqs);
-  if (grid.y > 65535 || grid.z > 65535) return PE_ERR_UNSUPPORTED_SIZE;
+  const long long total = tiles * n_kv_heads * n_seqs;
+  if (total <= 0 || total > (1ll << 30)) return PE_ERR_UNSUPPORTED_SIZE;
+  a.tiles = (int)tiles; a.n_seqs = n_seqs; a.work_counter = work_counter;
+  // two blocks fit on an SM (shared memory, tensor memory columns); no more blocks than items
+  const long long slots = 2ll * (n_sms > 0 ? n_sms : pe::kSMs);
+  dim3 grid((unsigned)(total < slots ? total : slots));
   pe::launch(prefill_umma_kernel, grid, 192, smem, stream, a, qmap, kmap, vmap);
   PE_LAUNCH_CHECK();
   return PE_OK;

@@ -278,6 +278,20 @@ def attention_umma_supported(dtype: torch.dtype, head_dim: int, n_heads: int, n_
     return dtype == torch.bfloat16 and bool(library().pe_attention_umma_supported(head_dim, n_heads, n_kv_heads))
 
 
+_WORK_COUNTERS = {}
+
+
+def _work_counter(device: torch.device) -> torch.Tensor:
+    """Two zero ints per (device, stream) for kernels that hand out work through a counter; the kernels
+    leave them zero.  Launches on one stream run one after the other, so they may share a counter."""
+    key = (device.index or 0, _stream())
+    t = _WORK_COUNTERS.get(key)
+    if t is None:
+        t = torch.zeros(2, dtype=torch.int32, device=device)
+        _WORK_COUNTERS[key] = t
+    return t
+
+
 def attention_umma_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_q: int, n_heads: int, n_kv_heads: int,
                            head_dim: int, scale: float, window: int, seq_qstart: torch.Tensor, seq_past: torch.Tensor,
                            seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int, k_pages: torch.Tensor,
@@ -289,7 +303,8 @@ def attention_umma_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_
     check(library().pe_attention_umma_prefill(
         _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), n_seqs, max_q, n_heads, n_kv_heads, head_dim,
         float(scale), int(window), _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot), _ptr(page_table),
-        page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages), _ptr(status), _stream()), "attention_umma_prefill")
+        page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages), sm_count(q.device), _ptr(_work_counter(q.device)), _ptr(status), _stream()),
+        "attention_umma_prefill")
     _count(1)
 
 
