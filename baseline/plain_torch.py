@@ -6,9 +6,8 @@ It uses library calls only (``F.linear`` in bfloat16, ``F.scaled_dot_product_att
 contiguous cache per batch) and none of this repository's kernels or classes.  The formulas are the
 reference's (pygguf_engine/model.py:462-496 attention with q/k-norm before RoPE, 232-251 split-half RoPE,
 839-846 SwiGLU, 1025-1042 pre-norm block, 2303-2304 wanted rows before the final norm); the residual stream,
-norms and rotation are float32 as there.  Random N(0, 0.02) weights are made on the device, one set of
-matrices per layer kind shared by all layers: time does not depend on the values, and memory stays free
-for the engine that is measured beside it.
+norms and rotation are float32 as there.  Random N(0, 0.02) weights are made on the device; every layer has
+matrices of its own, so that a decode step has to read them all from memory as a real model's step does.
 """
 from __future__ import annotations
 

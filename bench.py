@@ -170,7 +170,7 @@ def main():
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--no-baseline", action="store_true", help="skip the plain PyTorch model that vs_baseline divides by")
     ap.add_argument("--micro", type=str, default=None,
-                    help="time single kernels at the preset's sizes instead (gemm, prefill_attention, decode_attention, sampler) and print text")
+                    help="time single kernels at the preset's sizes instead (gemm, prefill_attention, decode_attention, rope_append, sampler) and print text")
     args = ap.parse_args()
 
     if args.gpus != 1:

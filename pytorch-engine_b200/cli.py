@@ -36,6 +36,8 @@ def build_parser() -> argparse.ArgumentParser:
     pr.add_argument("--prompt-file", type=str, default=None, help="file with one prompt per line (comma or space separated ids)")
     pr.add_argument("--random-prompts", type=str, default=None, metavar="LEN[,LEN...]",
                     help="uniform-random prompts of these lengths")
+    pr.add_argument("--prompt", action="append", default=[], metavar="TEXT",
+                    help="a prompt as text; needs tokenizer.json in the model folder (repeatable)")
     sm = p.add_argument_group("sampling")
     sm.add_argument("--max-tokens", type=int, default=512)
     sm.add_argument("--temperature", type=float, default=0.7)
@@ -51,6 +53,20 @@ def build_parser() -> argparse.ArgumentParser:
 
 def _ids(text: str) -> List[int]:
     return [int(t) for t in text.replace(",", " ").split()]
+
+
+def load_tokenizer(model_dir):
+    """The folder's ``tokenizer.json`` as a ``tokenizers.Tokenizer``, or None (no folder, no file, no package).
+    The engine itself works on token ids only; this is a convenience of the command line."""
+    import os
+
+    if not model_dir or not os.path.isfile(os.path.join(model_dir, "tokenizer.json")):
+        return None
+    try:
+        from tokenizers import Tokenizer
+    except ImportError:
+        return None
+    return Tokenizer.from_file(os.path.join(model_dir, "tokenizer.json"))
 
 
 def main(argv=None) -> int:
@@ -80,8 +96,16 @@ def main(argv=None) -> int:
         rng = random.Random(args.seed)
         vocab = getattr(cfg, "vocab_size")
         prompts += [[rng.randrange(vocab) for _ in range(n)] for n in _ids(args.random_prompts)]
+    tokenizer = None
+    if args.prompt:
+        tokenizer = load_tokenizer(args.model)
+        if tokenizer is None:
+            print("--prompt TEXT needs --model DIR with a tokenizer.json in it (and the `tokenizers` package); "
+                  "give token ids with --prompt-ids otherwise", file=sys.stderr)
+            return 2
+        prompts += [list(tokenizer.encode(text).ids) for text in args.prompt]
     if not prompts:
-        print("no prompt given (--prompt-ids, --prompt-file or --random-prompts)", file=sys.stderr)
+        print("no prompt given (--prompt-ids, --prompt-file, --random-prompts or --prompt)", file=sys.stderr)
         return 2
     kw = dict(dtype=args.dtype, max_context_len=args.ctx, max_batch=args.max_batch,
               max_step_tokens=args.max_step_tokens or None,
@@ -96,10 +120,11 @@ def main(argv=None) -> int:
             print(json.dumps({"request": i, "token_ids": r.token_ids, "prompt_tokens": r.prompt_tokens,
                               "completion_tokens": r.completion_tokens, "finish_reason": r.finish_reason,
                               "prefill_time_s": round(r.prefill_time_s, 6), "decode_time_s": round(r.decode_time_s, 6),
-                              "decode_tok_per_s": round(r.decode_tok_per_s, 2)}))
+                              "decode_tok_per_s": round(r.decode_tok_per_s, 2),
+                              **({"text": tokenizer.decode(r.token_ids)} if tokenizer is not None else {})}))
         else:
-            print(f"[{i}] {r.finish_reason} after {r.completion_tokens} tokens "
-                  f"({r.decode_tok_per_s:.1f} tok/s): {' '.join(map(str, r.token_ids))}")
+            shown = tokenizer.decode(r.token_ids) if tokenizer is not None else " ".join(map(str, r.token_ids))
+            print(f"[{i}] {r.finish_reason} after {r.completion_tokens} tokens ({r.decode_tok_per_s:.1f} tok/s): {shown}")
     return 0
 
 

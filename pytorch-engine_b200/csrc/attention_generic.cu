@@ -14,6 +14,7 @@
 // `split_keys` positions); its warps take the 32-key tiles of the range in turn and merge at the
 // end; a second kernel merges the ranges.  Which keys a partial result covers depends only on the
 // sequence's own length, never on what else is in the batch.
+#include "api.h"
 #include "common.cuh"
 
 namespace pe {

@@ -24,6 +24,7 @@
 // (K) and the transposed (V) ldmatrix reads conflict-free.  Rows of a page beyond the sequence's
 // length are not read as zeros: the cache never holds a non-finite value there (the append kernel
 // clears the rest of a page when it starts one), and their probabilities are exactly zero.
+#include "api.h"
 #include "common.cuh"
 #include "tma.cuh"
 

@@ -37,6 +37,7 @@
 // producer warp fetches the rank and hands it to the other warps through a two-slot ring in shared memory.
 // Barrier phases, the K/V rings and tensor memory carry over from item to item: every role counts items
 // and pages the same way.
+#include "api.h"
 #include "common.cuh"
 #include "tma.cuh"
 

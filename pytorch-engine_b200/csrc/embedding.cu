@@ -1,5 +1,6 @@
 // Token embedding: residual stream (float32) <- table[ids].
 // Reference formula: pygguf_engine/quant_kernels.py:1846-1847 (row gather, cast to float32).
+#include "api.h"
 #include "common.cuh"
 
 namespace pe {

@@ -17,6 +17,7 @@
 // (K not a multiple of 8, M > 16), as the reference uses a library product for its unquantised
 // linears (pygguf_engine/quant_kernels.py:1836).  The fused epilogue restates
 // pygguf_engine/quant_kernels.py:1467-1472 (silu(gate) * up in float32).
+#include "api.h"
 #include "common.cuh"
 
 namespace pe {
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(WARPS * 32, NT == 1 ? 16 / WARPS : 1) gemm_sma
 }
 
 template <int NT, bool PAIR, typename OutT>
-static int launch(const Args& a, cudaStream_t stream) {
+static int launch(const Args& a, int n_sms, cudaStream_t stream) {
   const int blocks = (a.N + 15) / 16;
   const int kblocks = (a.K + 31) / 32;
   constexpr int U = PAIR ? 2 : 4;
@@ -201,8 +202,8 @@ static int launch(const Args& a, cudaStream_t stream) {
   // M <= 8 kernels (128 registers) and 12 of the M <= 16 kernels (up to 168 registers) as long as their
   // blocks have at most 4 warps; a block of 8 would be alone on its SM.
   constexpr int kMaxWarps = NT == 1 ? 8 : 4;
-  const long long slots = (long long)kSMs * (NT == 1 ? 16 : 12);
-  const long long want_warps = (long long)kSMs * 24;
+  const long long slots = (long long)n_sms * (NT == 1 ? 16 : 12);
+  const long long want_warps = (long long)n_sms * 24;
   int warps = 1;
   while (warps < kMaxWarps && (long long)blocks * warps < want_warps && kblocks / (warps * 2) >= 2 * U) warps *= 2;
   // A second wave that fills less than half of the GPU costs more than longer K slices in one wave
@@ -226,9 +227,10 @@ extern "C" int pe_gemm_smallm_supported(int M, int N, int K) {
 }
 
 // out_f32 != 0: y is float32, else bfloat16.  pair_offset > 0: W has 2 * N rows, row n (gate) is paired with
-// row n + pair_offset (up) and y[m, n] = silu(x.gate_n) * (x.up_n).
+// row n + pair_offset (up) and y[m, n] = silu(x.gate_n) * (x.up_n).  n_sms: the device's SM count (it sizes the
+// split of K over a block's warps; 0: a B200's).
 extern "C" int pe_gemm_smallm(const void* x, long long ldx, const void* w, void* y, long long ldy, int M, int N, int K,
-                              int out_f32, int pair_offset, cudaStream_t stream) {
+                              int out_f32, int pair_offset, int n_sms, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return PE_OK;
   if (!pe_gemm_smallm_supported(M, N, K)) return PE_ERR_UNSUPPORTED_SIZE;
   if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || (ldx * 2) % 16) return PE_ERR_BAD_ARGUMENT;
@@ -236,11 +238,12 @@ extern "C" int pe_gemm_smallm(const void* x, long long ldx, const void* w, void*
   a.x = (const __nv_bfloat16*)x; a.ldx = ldx; a.w = (const __nv_bfloat16*)w; a.y = y; a.ldy = ldy;
   a.M = M; a.N = N; a.K = K; a.pair_offset = pair_offset;
   using namespace pe::smallm;
+  if (n_sms <= 0) n_sms = pe::kSMs;
   const bool pair = pair_offset > 0;
   if (M <= 8) {
-    if (pair) return out_f32 ? launch<1, true, float>(a, stream) : launch<1, true, __nv_bfloat16>(a, stream);
-    return out_f32 ? launch<1, false, float>(a, stream) : launch<1, false, __nv_bfloat16>(a, stream);
+    if (pair) return out_f32 ? launch<1, true, float>(a, n_sms, stream) : launch<1, true, __nv_bfloat16>(a, n_sms, stream);
+    return out_f32 ? launch<1, false, float>(a, n_sms, stream) : launch<1, false, __nv_bfloat16>(a, n_sms, stream);
   }
-  if (pair) return out_f32 ? launch<2, true, float>(a, stream) : launch<2, true, __nv_bfloat16>(a, stream);
-  return out_f32 ? launch<2, false, float>(a, stream) : launch<2, false, __nv_bfloat16>(a, stream);
+  if (pair) return out_f32 ? launch<2, true, float>(a, n_sms, stream) : launch<2, true, __nv_bfloat16>(a, n_sms, stream);
+  return out_f32 ? launch<2, false, float>(a, n_sms, stream) : launch<2, false, __nv_bfloat16>(a, n_sms, stream);
 }

@@ -17,6 +17,7 @@
 //
 // Every wait is bounded (tma.cuh); a wait that runs out records kStatusWaitTimedOut, every role
 // leaves its loop, and the block frees its TMEM before it returns.
+#include "api.h"
 #include "common.cuh"
 #include "tma.cuh"
 

@@ -21,6 +21,7 @@
 //
 // Every wait is bounded; a wait that runs out records kStatusWaitTimedOut, every role leaves its
 // loop, the pair meets at a cluster barrier and frees its tensor memory.
+#include "api.h"
 #include "common.cuh"
 #include "tma.cuh"
 

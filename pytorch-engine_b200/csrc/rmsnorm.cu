@@ -9,6 +9,7 @@
 //         written back to the stream (the residual add of the block).
 //         rows != nullptr: output row r is stream row rows[r] (+ delta row rows[r]); nothing is
 //         written back (the final norm on the rows whose logits are wanted).
+#include "api.h"
 #include "common.cuh"
 
 namespace pe {

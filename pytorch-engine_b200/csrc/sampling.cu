@@ -17,6 +17,7 @@
 // its largest entry); the second runs the filter chain on the candidates of a row, which hold
 // every entry that the row's top-k can keep.  A threshold search takes 8 sweeps of 4 bits with
 // per-thread counters (no atomics, fixed summation order) instead of 32 sweeps of one bit.
+#include "api.h"
 #include "common.cuh"
 
 namespace pe {

@@ -2,6 +2,7 @@
 // one row of the fused gate|up projection (gate first).
 // Reference formula: pygguf_engine/quant_kernels.py:1467-1472 (silu and product in float32).  The
 // reference's float16 row scale (1473-1474) cancels exactly and is not needed in bfloat16/float32.
+#include "api.h"
 #include "common.cuh"
 
 namespace pe {

@@ -49,7 +49,7 @@ _SIGNATURES = {
     "pe_repetition_penalty": [P, L, I, I, P, I, P, F, P],
     "pe_attention_mma": [I, P, L, P, L, I, I, I, I, I, F, I, P, P, P, P, I, I, P, P, P, I, I, I, P, P],
     "pe_attention_mma_supported": [I, I, I],
-    "pe_gemm_smallm": [P, L, P, P, L, I, I, I, I, I, P],
+    "pe_gemm_smallm": [P, L, P, P, L, I, I, I, I, I, I, P],
     "pe_gemm_smallm_supported": [I, I, I],
     "pe_gemm_umma": [P, L, P, P, L, I, I, I, I, I, I, P, P],
     "pe_gemm_umma_supported": [I, I, I, I],

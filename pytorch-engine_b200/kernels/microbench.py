@@ -172,4 +172,31 @@ def sampler(cfg, device, batches: Sequence[int] = (1, 8, 64)) -> None:
                   (f", two kernels {two:.1f} us" if two is not None else ", no two-kernel path"), flush=True)
 
 
-CASES: Dict[str, Callable] = {"gemm": gemm, "prefill_attention": prefill_attention, "decode_attention": decode_attention, "sampler": sampler}
+def rope_append(cfg, device, cases: Sequence[Sequence[int]] = ((2048, 1), (2048, 4), (512, 1), (8192, 2), (8, 8))) -> None:
+    """q/k-norm + rotation + append of a step of N tokens in B sequences (calls in a row: the rows it reads were
+    just written by the q|k|v product and sit in L2, as here)."""
+    nh, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    for n, b in cases:
+        ld = (nh + 2 * nkv) * d
+        qkv = torch.randn(n, ld, device=device).to(torch.bfloat16)
+        qw, kw = torch.ones(d, device=device), torch.ones(d, device=device)
+        cos, sin = torch.randn(8192, d // 2, device=device), torch.randn(8192, d // 2, device=device)
+        per = n // b
+        token_seq = torch.arange(n, device=device, dtype=torch.int32) // per
+        past = 4000 if per == 1 else 0
+        token_pos = (torch.arange(n, device=device, dtype=torch.int32) % per) + past
+        seq_slot = torch.arange(b, device=device, dtype=torch.int32)
+        qstart = torch.arange(b + 1, device=device, dtype=torch.int32) * per
+        pages_per = 8192 // 64
+        table = torch.arange(b * pages_per, device=device, dtype=torch.int32).view(b, pages_per)
+        kp = torch.zeros(b * pages_per, nkv, 64, d, device=device, dtype=torch.bfloat16)
+        vp = torch.zeros_like(kp)
+        status = torch.zeros(4, dtype=torch.int32, device=device)
+        us = time_in_a_row(lambda: ops.qk_norm_rope_append(qkv, n, nh, nkv, d, qw, kw, 1e-6, cos, sin, d, token_seq, token_pos,
+                                                           seq_slot, qstart, table, b * pages_per, kp, vp, True, status), calls=20)
+        moved = n * ld * 2 + n * (nh + nkv) * d * 2 + n * 2 * nkv * d * 2     # rows read, q and k written back, k and v to the cache
+        print(f"{n} tokens in {b} sequence(s), {nh} x {nkv} heads, d={d}: {us:.1f} us ({moved / us / 1e6:.2f} TB/s)  "
+              f"status {status.tolist()[0]}", flush=True)
+
+
+CASES: Dict[str, Callable] = {"rope_append": rope_append, "gemm": gemm, "prefill_attention": prefill_attention, "decode_attention": decode_attention, "sampler": sampler}

@@ -185,7 +185,7 @@ def gemm_smallm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, pair_o
           "gemm_smallm: shapes do not match")
     _need(pair_offset in (0, n), "gemm_smallm: pair_offset must be 0 or the output width")
     check(library().pe_gemm_smallm(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), out.stride(0), m, n, k,
-                                   1 if out.dtype == torch.float32 else 0, pair_offset, _stream()), "gemm_smallm")
+                                   1 if out.dtype == torch.float32 else 0, pair_offset, sm_count(x.device), _stream()), "gemm_smallm")
     _count(1)
 
 

@@ -116,3 +116,19 @@ def test_large_products_that_fill_their_waves_badly_go_to_the_library(pe):
     assert abs(fill(1536, 4096, 148) - 96 / 148) < 1e-9         # 96 tiles need two waves of 74
     assert fill(2048, 6144, 148) > 0.8 > fill(1024, 6144, 148)
     assert fill(1, 1, 2) == 1.0
+
+
+def test_cli_text_prompts_need_a_tokenizer_file(pe, tmp_path, capsys):
+    from importlib import import_module
+    cli = import_module("pytorch-engine_b200.cli")
+    assert cli.main(["--random", "tiny_a", "--write-random", str(tmp_path / "m")]) == 0
+    assert cli.load_tokenizer(str(tmp_path / "m")) is None
+    assert cli.main(["--model", str(tmp_path / "m"), "--prompt", "hello there"]) == 2
+    assert "tokenizer.json" in capsys.readouterr().err
+    tokenizers = pytest.importorskip("tokenizers")
+    vocab = {"[UNK]": 0, "hello": 1, "there": 2}
+    tok = tokenizers.Tokenizer(tokenizers.models.WordLevel(vocab, unk_token="[UNK]"))
+    tok.pre_tokenizer = tokenizers.pre_tokenizers.Whitespace()
+    tok.save(str(tmp_path / "m" / "tokenizer.json"))
+    loaded = cli.load_tokenizer(str(tmp_path / "m"))
+    assert loaded.encode("hello there you").ids == [1, 2, 0]
