@@ -85,6 +85,57 @@ def gemm(cfg, device, rows: Sequence[int] = (2048, 4096, 1024)) -> None:
     print("status word", status.tolist(), flush=True)
 
 
+def time_in_a_graph(fns: Sequence[Callable[[int], None]], copies: int, rounds: int = 5) -> List[float]:
+    """Microseconds per call of each callable ``f(i)`` (``i``: which copy of the operands to use), as one CUDA
+    graph of ``copies`` calls each: no host time between the kernels, and with copies that together exceed
+    L2 every call streams its operands from memory.  Median of ``rounds`` replays."""
+    out = []
+    for f in fns:
+        for i in range(copies):
+            f(i)
+        torch.cuda.synchronize()
+        stream = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(copies):
+                f(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(rounds):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3 / copies)
+        out.append(sorted(times)[len(times) // 2])
+    return out
+
+
+def gemm_mid(cfg, device, rows: Sequence[int] = (16, 32, 64, 128)) -> None:
+    """Products of 9..128 rows, which the engine gives to the library: the library product and this package's
+    many-row kernel, each as a CUDA graph of calls that rotate over copies of W larger than L2 together (a single
+    call of 15 us cannot be timed from the host: preparing a launch takes as long)."""
+    status = torch.zeros(4, dtype=torch.int32, device=device)
+    h, i = cfg.hidden_size, cfg.intermediate_size
+    qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+    shapes = [("q|k|v", qkv, h), ("o", h, cfg.num_attention_heads * cfg.head_dim), ("down", h, i), ("lm_head", cfg.vocab_size, h)]
+    for name, n, k in shapes:
+        copies = max(2, min(12, -(-(320 << 20) // (n * k * 2))))
+        ws = [torch.randn(n, k, device=device).to(torch.bfloat16) for _ in range(copies)]
+        for m in rows:
+            x = torch.randn(m, k, device=device).to(torch.bfloat16)
+            out = torch.empty(m, n, device=device, dtype=torch.bfloat16)
+            t = time_in_a_graph([lambda c: torch.mm(x, ws[c].T, out=out), lambda c: ops.gemm_umma(x, ws[c], out, status)], copies)
+            mb = n * k * 2 / 1e6
+            print(f"M={m} {name} N={n} K={k} ({mb:.0f} MB x {copies} copies): library {t[0]:.1f} us ({mb / t[0]:.2f} TB/s)  "
+                  f"many-row kernel {t[1]:.1f} us", flush=True)
+        del ws
+    print("status word", status.tolist(), flush=True)
+
+
 def prefill_attention(cfg, device, lengths: Sequence[int] = (2048, 4096, 8192, 512)) -> None:
     """One prompt through the tcgen05 prefill attention and through the mma.sync one."""
     nh, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
@@ -199,4 +250,4 @@ def rope_append(cfg, device, cases: Sequence[Sequence[int]] = ((2048, 1), (2048,
               f"status {status.tolist()[0]}", flush=True)
 
 
-CASES: Dict[str, Callable] = {"rope_append": rope_append, "gemm": gemm, "prefill_attention": prefill_attention, "decode_attention": decode_attention, "sampler": sampler}
+CASES: Dict[str, Callable] = {"rope_append": rope_append, "gemm_mid": gemm_mid, "gemm": gemm, "prefill_attention": prefill_attention, "decode_attention": decode_attention, "sampler": sampler}
