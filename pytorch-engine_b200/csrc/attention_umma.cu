@@ -183,6 +183,31 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+// Blackwell's two-wide float32 arithmetic and three-input maximum: the softmax threads are bound by the number
+// of instructions they issue, not by any one pipe.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -458,7 +483,8 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
 #pragma unroll
           for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(sv[h][c]));
+            for (int c = 0; c < 16; ++c)
+              m4[c & 3] = max3(m4[c & 3], __uint_as_float(sv[h][2 * c]), __uint_as_float(sv[h][2 * c + 1]));
           mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * a.scale_log2;   // the scale is positive
         } else {
 #pragma unroll
@@ -494,30 +520,31 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
         }
         if (grow) m_ref = mx;
         const float base = (m_ref == -INFINITY) ? 0.f : m_ref;
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};   // four chains (see the maximum); summed in a fixed order below
+        uint64_t sum4[4] = {0ull, 0ull, 0ull, 0ull};   // four chains of two-wide sums; added up in a fixed order below
         // P = exp2(score - reference) as bfloat16 pairs, back into tensor memory where S of this page was
-        // (this thread has read all of its S row): the P.V product takes its A operand from there
+        // (this thread has read all of its S row): the P.V product takes its A operand from there.  Scale and
+        // reference go in as one two-wide multiply-add per pair of scores (masked scores are scaled already).
         uint32_t pw[32];
-        auto exps = [&](auto exponent) {
+        const float sc = whole ? a.scale_log2 : 1.0f, nb = -base;
+        const uint64_t sc2 = pack_f32x2(sc, sc), nb2 = pack_f32x2(nb, nb);
 #pragma unroll
-          for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              const float p0 = fast_exp2(exponent(__uint_as_float(sv[h][2 * c])));
-              const float p1 = fast_exp2(exponent(__uint_as_float(sv[h][2 * c + 1])));
-              sum4[c & 3] += p0 + p1;
-              pw[h * 16 + c] = pack2(p0, p1);
-            }
-        };
-        if (whole) {
-          const float sc = a.scale_log2, nb = -base;
-          exps([sc, nb](float s) { return fmaf(s, sc, nb); });
-        } else {
-          exps([base](float s) { return s - base; });
-        }
+          for (int c = 0; c < 16; ++c) {
+            float x0, x1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[h][2 * c]), __uint_as_float(sv[h][2 * c + 1])), sc2, nb2), x0, x1);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            sum4[c & 3] = add_f32x2(sum4[c & 3], pack_f32x2(p0, p1));
+            pw[h * 16 + c] = pack2(p0, p1);
+          }
         tmem_st32(tmem_base + st * BN + lane_off, pw);
         tmem_st_wait();
-        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        {
+          float s0, s1, s2, s3, s4, s5, s6, s7;
+          unpack_f32x2(sum4[0], s0, s1); unpack_f32x2(sum4[1], s2, s3);
+          unpack_f32x2(sum4[2], s4, s5); unpack_f32x2(sum4[3], s6, s7);
+          l += ((s0 + s1) + (s2 + s3)) + ((s4 + s5) + (s6 + s7));
+        }
         fence_before_sync();
         tma::mbar_arrive(&p_ready[st]);
       }
