@@ -2,7 +2,7 @@
 """Benchmark: decode tokens/s of a Qwen3-8B-shaped model (random weights, bfloat16) on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --micro gemm|prefill_attention|decode_attention|sampler     (single kernels, text output)
+    python bench.py --micro gemm|gemm_mid|prefill_attention|decode_attention|rope_append|sampler   (single kernels, text)
 
 A step is one decode step: every live sequence gets one token (model step + sampler).  The default
 run has the layer sizes of the Qwen3-8B shape, a batch of 8 and a context of 4,096.  One JSON line
