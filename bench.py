@@ -8,11 +8,16 @@ A step is one decode step: every live sequence gets one token (model step + samp
 run has the layer sizes of the Qwen3-8B shape, a batch of 8 and a context of 4,096.  One JSON line
 is printed: ``value`` is decoded tokens/s timed on the device with CUDA events; ``e2e`` is the same
 through the Python entry point (``Engine.stream_tokens``: host token ids in, host token ids out
-every step; W untimed decode steps after the prompts, then K timed ones); ``prefill`` is one
-2,048-token prompt; ``roofline`` is the bytes a decode step must read (every weight once, the cache
-of the live requests) over its time; ``points`` holds decode at batch 1 and 64.  For the device-timed decode numbers the cache is brought to the wanted length by
-reserving pages over storage filled with random values (what a decode step costs does not depend
-on the values); the end-to-end number runs real prompts through the public API.
+every step; untimed decode steps after the prompts (at least 48: the clocks need them after a whole
+batch of prompts), then K timed ones, with per-step host times and the clocks seen); ``prefill`` is
+one 2,048-token prompt; ``roofline`` is the bytes a decode step must read (every weight once, the
+cache of the live requests) over its time; ``points`` holds decode at batch 1 and 64; ``baseline``
+and ``vs_baseline`` come from a plain PyTorch model of the same shape timed on the same GPU
+(baseline/plain_torch.py).  For the device-timed decode numbers the cache is brought to the wanted
+length by reserving pages over storage filled with random values (what a decode step costs does not
+depend on the values); the end-to-end number runs real prompts through the public API.
+``--impl reference`` runs the unmodified reference instead (baseline/reference_arm.py: its own
+engine on an F16 GGUF of the same shape, the requests one after another) and prints the same keys.
 """
 import argparse
 import importlib
@@ -186,7 +191,7 @@ def main():
     pe = importlib.import_module("pytorch-engine_b200")
     ops = pe.kernels.ops
     if args.micro:
-        micro = importlib.import_module("pytorch-engine_b200.kernels.microbench")
+        import bench_micro as micro
         if args.micro not in micro.CASES:
             print(f"bench.py: --micro takes one of {sorted(micro.CASES)}")
             return 2

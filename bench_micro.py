@@ -1,4 +1,5 @@
 """Timings of single kernels at the sizes of a configuration, printed as text (``bench.py --micro NAME``).
+It sits beside ``bench.py``, outside the package: the package holds what generation runs.
 
 Each case is timed with CUDA events on the launching stream after warm-up.  Cases that compare
 kernels call them in turn inside one loop, so that all see the same clocks, and flush L2 between
@@ -14,7 +15,9 @@ from typing import Callable, Dict, List, Sequence
 
 import torch
 
-from . import ops
+import importlib
+
+ops = importlib.import_module("pytorch-engine_b200.kernels.ops")
 
 
 def _flush_buffer(device) -> torch.Tensor:
