@@ -57,6 +57,12 @@ int pe_gemm_umma(const void* x, long long ldx, const void* w, void* y, long long
 int pe_gemm_umma2_supported(int M, int N, int K, int pair_offset);
 int pe_gemm_umma2(const void* x, long long ldx, const void* w, void* y, long long ldy, int M, int N, int K,
     int out_f32, int pair_offset, int n_sms, int* status, cudaStream_t stream);
+int pe_gemm_umma2_qkv_rope_supported(int M, int K, int n_heads, int n_kv_heads, int head_dim, int rotary_dim);
+int pe_gemm_umma2_qkv_rope(const void* x, long long ldx, const void* w, void* qkv, long long ld, int M, int K,
+    int n_heads, int n_kv_heads, int head_dim, const float* q_norm_w, const float* k_norm_w, float eps,
+    const float* cos_table, const float* sin_table, int rotary_dim, int table_rows, const int* token_seq,
+    const int* token_pos, const int* seq_slot, const int* seq_qstart, const int* page_table, int table_stride,
+    int num_pages, void* k_pages, void* v_pages, int write_cache, int n_sms, int* status, cudaStream_t stream);
 
 // rmsnorm.cu
 int pe_rmsnorm_residual(int dtype, float* residual, const void* delta, const float* weight, void* out,

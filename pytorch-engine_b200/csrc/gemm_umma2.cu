@@ -39,13 +39,32 @@ constexpr int kBytesA = KBS * kTileA, kBytesB = KBS * kTileB, kStage = kBytesA +
 constexpr int kTmemCols = 512;
 constexpr int kThreads = 192;
 
+// Mode 3: the product is the fused q|k|v projection of an attention layer with head size 128, and the epilogue
+// does what csrc/rope_append.cu does in a kernel of its own: per-head q/k RMSNorm, rotary encoding, q written to
+// the output rows, k and v appended to the paged cache.  A 256-column tile is two whole heads and an epilogue
+// thread owns a token's row of it, so everything a head needs is in that thread's lane of tensor memory.
+struct RopeFuse {
+  int n_heads, n_kv_heads;
+  const float* q_norm_w;   // [128] or null
+  const float* k_norm_w;
+  float eps;
+  const float* cos_table;  // [table_rows, 64] or null (no rotation)
+  const float* sin_table;
+  int table_rows;
+  const int* token_seq; const int* token_pos; const int* seq_slot; const int* seq_qstart;
+  const int* page_table; int table_stride, num_pages;
+  __nv_bfloat16* k_pages; __nv_bfloat16* v_pages;   // [num_pages, n_kv_heads, 64, 128]
+  int write_cache;
+};
+
 struct Params {
   int M, N, K;
   void* y; long long ldy;
-  int mode;               // 0: bfloat16, 1: float32, 2: silu(gate) * up -> bfloat16
+  int mode;               // 0: bfloat16, 1: float32, 2: silu(gate) * up -> bfloat16, 3: q|k|v with RopeFuse
   int pair_offset;
   int m_tiles, n_tiles, n_per_tile;
   int* status;
+  RopeFuse rope;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -154,6 +173,140 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ float bf16_round(uint32_t bits) {
+  return __bfloat162float(__float2bfloat16_rn(__uint_as_float(bits)));
+}
+
+// The epilogue of mode 3 for one token row of a 256-column tile (two heads of 128 features).  Formulas and order
+// as csrc/rope_append.cu (pygguf_engine/model.py:471-474 q/k-norm before RoPE, not on v; 232-241 split-half
+// rotation; 482-483 append): the accumulator is rounded to bfloat16 first (the value the projection would have
+// stored), the norm's sum runs over those values, norm and rotation are one float32 computation, the result is
+// rounded once.  Every thread of the warp runs every tensor-memory load; only live rows store.
+__device__ __forceinline__ void rope_epilogue(const Params& p, int row, int n0, uint32_t t_row) {
+  const RopeFuse& r = p.rope;
+  constexpr int D = 128, HALF = 64;
+  const bool live = row < p.M;
+  int pos = 0;
+  if (live) pos = r.token_pos[row];
+  const bool rotates = r.cos_table != nullptr;
+  const bool pos_ok = !rotates || (pos >= 0 && pos < r.table_rows);
+  if (live && !pos_ok) report(p.status, kStatusPositionOutOfRange, row, pos, r.table_rows);
+#pragma unroll 1
+  for (int h = 0; h < BN / D; ++h) {
+    const int col0 = n0 + h * D;
+    if (col0 >= p.N) break;
+    const int head = col0 / D;
+    const bool is_q = head < r.n_heads;
+    const bool is_k = !is_q && head < r.n_heads + r.n_kv_heads;
+    const int kv_head = is_q ? 0 : (is_k ? head - r.n_heads : head - r.n_heads - r.n_kv_heads);
+    const uint32_t t_head = t_row + h * D;
+    const float* w = is_q ? r.q_norm_w : (is_k ? r.k_norm_w : nullptr);
+    const bool wanted = is_q || r.write_cache;            // k and v of a layer that only reads a cache go nowhere
+    // where the row goes: q into the output rows, k and v into their page of the cache
+    __nv_bfloat16* dst = nullptr;
+    if (live && pos_ok && wanted) {
+      if (is_q) {
+        dst = reinterpret_cast<__nv_bfloat16*>(p.y) + (size_t)row * p.ldy + col0;
+      } else {
+        const int seq = r.token_seq[row];
+        const int slot = r.seq_slot[seq];
+        const int logical = pos / kPageTokens;
+        if (pos < 0 || logical >= r.table_stride) {
+          report(p.status, kStatusPositionOutOfRange, row, pos, r.table_stride * kPageTokens);
+        } else {
+          const int page = r.page_table[(size_t)slot * r.table_stride + logical];
+          if (page < 0 || page >= r.num_pages) {
+            report(p.status, kStatusPageOutOfRange, row, page, r.num_pages);
+          } else {
+            const int off = pos % kPageTokens;
+            dst = (is_k ? r.k_pages : r.v_pages) + (((size_t)page * r.n_kv_heads + kv_head) * kPageTokens + off) * D;
+            // rows of the page beyond the sequence's last key must hold finite values: the sequence's last token of
+            // this step clears the rest of its page when it starts the page or ends a multi-token step
+            const int q_begin = r.seq_qstart[seq], q_end = r.seq_qstart[seq + 1];
+            if (row + 1 == q_end && off + 1 < kPageTokens && (off == 0 || q_end - q_begin > 1)) {
+              uint4* rest = reinterpret_cast<uint4*>(dst + D);
+              const int n16 = (kPageTokens - 1 - off) * D / 8;
+              for (int i = 0; i < n16; ++i) rest[i] = make_uint4(0, 0, 0, 0);
+            }
+          }
+        }
+      }
+    }
+    // the norm's scale: sum of squares over the head, in four chains added up in a fixed order
+    float inv = 1.f;
+    if (w != nullptr) {
+      float ss[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld32(t_head + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float x = bf16_round(v[j]);
+          ss[j & 3] = fmaf(x, x, ss[j & 3]);
+        }
+      }
+      inv = rsqrtf(((ss[0] + ss[1]) + (ss[2] + ss[3])) / (float)D + r.eps);
+    }
+    // features j and j + 64 together, 32 pairs at a time
+#pragma unroll 1
+    for (int c = 0; c < HALF; c += 32) {
+      uint32_t a[32], b[32];
+      __syncwarp();
+      tmem_ld32(t_head + c, a);
+      tmem_ld32(t_head + HALF + c, b);
+      tmem_ld_wait();
+      if (dst != nullptr) {
+        uint32_t o1[16], o2[16];
+        const bool rot = rotates && !(!is_q && !is_k);
+        const float4* cs = rot ? reinterpret_cast<const float4*>(r.cos_table + (size_t)pos * HALF + c) : nullptr;
+        const float4* sn = rot ? reinterpret_cast<const float4*>(r.sin_table + (size_t)pos * HALF + c) : nullptr;
+        const float4* w1 = w ? reinterpret_cast<const float4*>(w + c) : nullptr;
+        const float4* w2 = w ? reinterpret_cast<const float4*>(w + HALF + c) : nullptr;
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          float x1[4], x2[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            x1[e] = bf16_round(a[4 * q4 + e]);
+            x2[e] = bf16_round(b[4 * q4 + e]);
+          }
+          if (w) {
+            const float4 wa = w1[q4], wb = w2[q4];
+            x1[0] = x1[0] * inv * wa.x; x1[1] = x1[1] * inv * wa.y; x1[2] = x1[2] * inv * wa.z; x1[3] = x1[3] * inv * wa.w;
+            x2[0] = x2[0] * inv * wb.x; x2[1] = x2[1] * inv * wb.y; x2[2] = x2[2] * inv * wb.z; x2[3] = x2[3] * inv * wb.w;
+          }
+          float y1[4], y2[4];
+          if (rot) {
+            const float4 cv = cs[q4], sv = sn[q4];
+            const float cc[4] = {cv.x, cv.y, cv.z, cv.w}, ss4[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              y1[e] = x1[e] * cc[e] - x2[e] * ss4[e];
+              y2[e] = x2[e] * cc[e] + x1[e] * ss4[e];
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { y1[e] = x1[e]; y2[e] = x2[e]; }
+          }
+          o1[2 * q4] = pack2(y1[0], y1[1]); o1[2 * q4 + 1] = pack2(y1[2], y1[3]);
+          o2[2 * q4] = pack2(y2[0], y2[1]); o2[2 * q4 + 1] = pack2(y2[2], y2[3]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          reinterpret_cast<uint4*>(dst + c)[j] = make_uint4(o1[4 * j], o1[4 * j + 1], o1[4 * j + 2], o1[4 * j + 3]);
+          reinterpret_cast<uint4*>(dst + HALF + c)[j] = make_uint4(o2[4 * j], o2[4 * j + 1], o2[4 * j + 2], o2[4 * j + 3]);
+        }
+      }
+    }
+  }
+}
+
+// ROPE: the instantiation that carries mode 3's epilogue (it needs 231 registers where the plain epilogues need 94;
+// the plain products keep a kernel of their own).
+template <bool ROPE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma2_kernel(Params p, const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap) {
   extern __shared__ char smem_raw[];
@@ -269,7 +422,9 @@ gemm_umma2_kernel(Params p, const __grid_constant__ CUtensorMap amap, const __gr
       fence_after_sync();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + ab * BN + ((uint32_t)(quarter * 32) << 16);
-      if (p.mode == 2) {
+      if (ROPE) {
+        rope_epilogue(p, row, n0, t_row);
+      } else if (p.mode == 2) {
         __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + (size_t)row * p.ldy + n0;
 #pragma unroll 1
         for (int c = 0; c < 128; c += 32) {
@@ -356,6 +511,12 @@ extern "C" int pe_gemm_umma2_supported(int M, int N, int K, int pair_offset) {
   return 1;
 }
 
+namespace pe {
+namespace umma2 {
+static int launch_pair(Params p, const void* x, long long ldx, const void* w, int n_sms, cudaStream_t stream);
+}
+}
+
 // The arguments of pe_gemm_umma (gemm_umma.cu); n_sms is rounded down to pairs; K a multiple of 64.
 extern "C" int pe_gemm_umma2(const void* x, long long ldx, const void* w, void* y, long long ldy, int M, int N, int K,
                              int out_f32, int pair_offset, int n_sms, int* status, cudaStream_t stream) {
@@ -367,6 +528,51 @@ extern "C" int pe_gemm_umma2(const void* x, long long ldx, const void* w, void* 
   p.M = M; p.N = N; p.K = K; p.y = y; p.ldy = ldy; p.status = status;
   p.mode = pair_offset > 0 ? 2 : (out_f32 ? 1 : 0);
   p.pair_offset = pair_offset;
+  p.rope = RopeFuse();
+  return launch_pair(p, x, ldx, w, n_sms, stream);
+}
+
+// 1 if pe_gemm_umma2_qkv_rope takes the layer: head size 128, the whole head rotated (or none of it).
+extern "C" int pe_gemm_umma2_qkv_rope_supported(int M, int K, int n_heads, int n_kv_heads, int head_dim, int rotary_dim) {
+  if (head_dim != 128 || n_heads < 1 || n_kv_heads < 0) return 0;
+  if (rotary_dim != 0 && rotary_dim != head_dim) return 0;
+  return pe_gemm_umma2_supported(M, (n_heads + 2 * n_kv_heads) * head_dim, K, 0);
+}
+
+// The fused q|k|v projection with the epilogue of csrc/rope_append.cu (see RopeFuse): qkv[:, :n_heads * 128] gets
+// the normalised, rotated queries; keys and values go to the cache only (write_cache) and not to qkv.
+// Arguments as pe_qk_norm_rope_append; rotary_dim 0 or cos_table null: no rotation.
+extern "C" int pe_gemm_umma2_qkv_rope(const void* x, long long ldx, const void* w, void* qkv, long long ld, int M, int K,
+                                      int n_heads, int n_kv_heads, int head_dim, const float* q_norm_w,
+                                      const float* k_norm_w, float eps, const float* cos_table, const float* sin_table,
+                                      int rotary_dim, int table_rows, const int* token_seq, const int* token_pos,
+                                      const int* seq_slot, const int* seq_qstart, const int* page_table, int table_stride,
+                                      int num_pages, void* k_pages, void* v_pages, int write_cache, int n_sms, int* status,
+                                      cudaStream_t stream) {
+  using namespace pe::umma2;
+  if (M <= 0) return PE_OK;
+  if (cos_table == nullptr) rotary_dim = 0;
+  if (!pe_gemm_umma2_qkv_rope_supported(M, K, n_heads, n_kv_heads, head_dim, rotary_dim) || n_sms < 2) return PE_ERR_UNSUPPORTED_SIZE;
+  if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || (ldx * 2) % 16 || ((uintptr_t)qkv % 16) || (ld * 2) % 16 ||
+      ((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16) || ((uintptr_t)q_norm_w % 16) || ((uintptr_t)k_norm_w % 16) ||
+      ((uintptr_t)cos_table % 16) || ((uintptr_t)sin_table % 16))
+    return PE_ERR_BAD_ARGUMENT;
+  if (write_cache && (page_table == nullptr || k_pages == nullptr || v_pages == nullptr)) return PE_ERR_BAD_ARGUMENT;
+  Params p;
+  p.M = M; p.N = (n_heads + 2 * n_kv_heads) * head_dim; p.K = K; p.y = qkv; p.ldy = ld; p.status = status;
+  p.mode = 3;
+  p.pair_offset = 0;
+  RopeFuse& r = p.rope;
+  r.n_heads = n_heads; r.n_kv_heads = n_kv_heads; r.q_norm_w = q_norm_w; r.k_norm_w = k_norm_w; r.eps = eps;
+  r.cos_table = rotary_dim > 0 ? cos_table : nullptr; r.sin_table = rotary_dim > 0 ? sin_table : nullptr;
+  r.table_rows = table_rows; r.token_seq = token_seq; r.token_pos = token_pos; r.seq_slot = seq_slot;
+  r.seq_qstart = seq_qstart; r.page_table = page_table; r.table_stride = table_stride; r.num_pages = num_pages;
+  r.k_pages = (__nv_bfloat16*)k_pages; r.v_pages = (__nv_bfloat16*)v_pages; r.write_cache = write_cache;
+  return launch_pair(p, x, ldx, w, n_sms, stream);
+}
+
+static int pe::umma2::launch_pair(Params p, const void* x, long long ldx, const void* w, int n_sms, cudaStream_t stream) {
+  const int M = p.M, N = p.N, K = p.K, pair_offset = p.pair_offset;
   p.n_per_tile = pair_offset > 0 ? BNH : BN;
   p.m_tiles = (M + 2 * BM - 1) / (2 * BM);
   p.n_tiles = (N + p.n_per_tile - 1) / p.n_per_tile;
@@ -378,7 +584,9 @@ extern "C" int pe_gemm_umma2(const void* x, long long ldx, const void* w, void* 
   const size_t smem = 1024 + (size_t)STAGES * kStage;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t ce = cudaFuncSetAttribute(gemm_umma2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t ce = cudaFuncSetAttribute(gemm_umma2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (ce == cudaSuccess)
+      ce = cudaFuncSetAttribute(gemm_umma2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (ce != cudaSuccess) return (int)ce;
     attr_set = true;
   }
@@ -398,7 +606,8 @@ extern "C" int pe_gemm_umma2(const void* x, long long ldx, const void* w, void* 
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pe::pdl_enabled() ? 2 : 1;
-  cudaError_t ce = cudaLaunchKernelEx(&cfg, gemm_umma2_kernel, p, amap, bmap);
+  cudaError_t ce = p.mode == 3 ? cudaLaunchKernelEx(&cfg, gemm_umma2_kernel<true>, p, amap, bmap)
+                               : cudaLaunchKernelEx(&cfg, gemm_umma2_kernel<false>, p, amap, bmap);
   if (ce != cudaSuccess) return (int)ce;
   PE_LAUNCH_CHECK();
   return PE_OK;

@@ -55,6 +55,8 @@ _SIGNATURES = {
     "pe_gemm_umma_supported": [I, I, I, I],
     "pe_gemm_umma2": [P, L, P, P, L, I, I, I, I, I, I, P, P],
     "pe_gemm_umma2_supported": [I, I, I, I],
+    "pe_gemm_umma2_qkv_rope_supported": [I, I, I, I, I, I],
+    "pe_gemm_umma2_qkv_rope": [P, L, P, P, L, I, I, I, I, I, P, P, F, P, P, I, I, P, P, P, P, P, I, I, P, P, I, I, P, P],
     "pe_attention_mma_decode_blocks_per_sm": [I],
     "pe_attention_umma_prefill": [P, L, L, P, L, I, I, I, I, I, F, I, P, P, P, P, I, I, P, P, I, P, P, P],
     "pe_attention_umma_supported": [I, I, I],

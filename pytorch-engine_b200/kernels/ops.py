@@ -247,6 +247,37 @@ def gemm_umma2(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, status:
     _count(1)
 
 
+def gemm_umma2_qkv_rope_supported(x: torch.Tensor, weight: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                                  rotary_dim: int) -> bool:
+    """Whether the q|k|v projection of this layer can run with q/k-norm, rotation and cache append in its epilogue
+    (csrc/gemm_umma2.cu, mode 3): bfloat16, head size 128, the whole head rotated or none of it, K % 64 == 0."""
+    if not gemm_umma2_supported(x, weight):
+        return False
+    return bool(library().pe_gemm_umma2_qkv_rope_supported(x.shape[0], x.shape[1], n_heads, n_kv_heads, head_dim, rotary_dim))
+
+
+def gemm_umma2_qkv_rope(x: torch.Tensor, weight: torch.Tensor, qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                        q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
+                        cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int, token_seq: torch.Tensor,
+                        token_pos: torch.Tensor, seq_slot: torch.Tensor, seq_qstart: torch.Tensor,
+                        page_table: Optional[torch.Tensor], num_pages: int, k_pages: Optional[torch.Tensor],
+                        v_pages: Optional[torch.Tensor], write_cache: bool, status: torch.Tensor) -> None:
+    """``x @ weight^T`` (the fused q|k|v projection) with what ``qk_norm_rope_append`` does in the product's epilogue:
+    ``qkv[:, :n_heads * head_dim]`` gets the normalised, rotated queries; keys and values go to the cache only."""
+    _need(gemm_umma2_qkv_rope_supported(x, weight, n_heads, n_kv_heads, head_dim, rotary_dim if cos is not None else 0),
+          "gemm_umma2_qkv_rope: needs bfloat16, head size 128, whole-head rotation, K % 64 == 0")
+    _need(qkv.dtype == torch.bfloat16 and qkv.stride(-1) == 1 and qkv.shape[0] == x.shape[0], "gemm_umma2_qkv_rope: qkv rows")
+    _need(weight.shape[0] == (n_heads + 2 * n_kv_heads) * head_dim, "gemm_umma2_qkv_rope: weight rows")
+    m, k = x.shape
+    check(library().pe_gemm_umma2_qkv_rope(
+        _ptr(x), x.stride(0), _ptr(weight), _ptr(qkv), qkv.stride(0), m, k, n_heads, n_kv_heads, head_dim,
+        _ptr(q_norm_w), _ptr(k_norm_w), float(eps), _ptr(cos), _ptr(sin), rotary_dim if cos is not None else 0,
+        0 if cos is None else cos.shape[0], _ptr(token_seq), _ptr(token_pos), _ptr(seq_slot), _ptr(seq_qstart),
+        _ptr(page_table), 0 if page_table is None else page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages),
+        1 if write_cache else 0, sm_count(x.device), _ptr(status), _stream()), "gemm_umma2_qkv_rope")
+    _count(1)
+
+
 def decode_ranges(slots: int, pairs: int, max_kv_len: int, split_keys: int) -> tuple:
     """(split_keys, max_splits, min_range_keys) for a decode attention whose SMs hold ``slots`` blocks at a
     time and that has ``pairs`` (sequence, kv head) pairs; split_keys 0 means that each sequence's keys

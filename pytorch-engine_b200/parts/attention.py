@@ -94,7 +94,40 @@ class GQAttention:
         rt = self.runtime
         n = x.shape[0]
         qkv = ctx.buffer("attn.qkv", (n, self.qkv_dim), rt.dtype)
-        rt.linear(x, self.qkv, out=qkv)
+        where = (ctx.token_seq, ctx.token_pos, ctx.seq_slot, ctx.seq_qstart, view.page_table, view.num_pages,
+                 view.k_pages, view.v_pages)
+        if self.fuses_rope_into_product(x, rt):
+            # many rows: q/k-norm, rotation and the cache append ride in the epilogue of the q|k|v product (its
+            # 256-column tiles are two whole heads), so q|k|v is never written and read again in between
+            cos = sin = None
+            rotary_dim = 0
+            if self.position is not None:
+                cos, sin, rotary_dim = self.position.tables()
+            ops.gemm_umma2_qkv_rope(x, self.qkv, qkv, self.n_heads, self.n_kv_heads, self.head_dim, self.q_norm, self.k_norm,
+                                    self.eps, cos, sin, rotary_dim, *where, writes_cache, rt.status)
+        else:
+            rt.linear(x, self.qkv, out=qkv)
+            self.norm_rotate_append(qkv, n, ctx, view, writes_cache)
+        out = ctx.buffer("attn.out", (n, self.n_heads * self.head_dim), rt.dtype)
+        self.attend(qkv, out, ctx, view)
+        delta = ctx.buffer("attn.delta", (n, self.hidden), rt.dtype)
+        rt.linear(out, self.o_proj, out=delta)
+        return delta
+
+    def fuses_rope_into_product(self, x: torch.Tensor, rt) -> bool:
+        """Whether this step's q|k|v product takes norm, rotation and append into its epilogue: the many-row tcgen05
+        pair kernel must be the one that runs (as ``Runtime.linear`` would decide), the position encoding one that
+        it can apply (rotary tables over the whole head, or none), the head size 128."""
+        if rt.gemm_backend is not None or not rt.fuse_qkv_rope or not rt.pair_gemm or not rt.takes_large_gemm(x, self.qkv):
+            return False
+        if self.position is not None and not self.fused_position:
+            return False
+        rotary_dim = self.position.tables()[2] if self.position is not None else 0
+        return ops.gemm_umma2_qkv_rope_supported(x, self.qkv, self.n_heads, self.n_kv_heads, self.head_dim, rotary_dim)
+
+    def norm_rotate_append(self, qkv: torch.Tensor, n: int, ctx, view, writes_cache: bool) -> None:
+        """q/k-norm, position encoding and cache append on the projected rows, as kernels of their own."""
+        rt = self.runtime
         where = (ctx.token_seq, ctx.token_pos, ctx.seq_slot, ctx.seq_qstart, view.page_table, view.num_pages,
                  view.k_pages, view.v_pages)
         shape = (qkv, n, self.n_heads, self.n_kv_heads, self.head_dim)
@@ -115,11 +148,6 @@ class GQAttention:
                                 qkv[:, qd:qd + kd].view(n, self.n_kv_heads, self.head_dim), ctx.token_pos)
             if writes_cache:
                 ops.qk_norm_rope_append(*shape, None, None, self.eps, None, None, 0, *where, True, rt.status)
-        out = ctx.buffer("attn.out", (n, self.n_heads * self.head_dim), rt.dtype)
-        self.attend(qkv, out, ctx, view)
-        delta = ctx.buffer("attn.delta", (n, self.hidden), rt.dtype)
-        rt.linear(out, self.o_proj, out=delta)
-        return delta
 
     def attend(self, q: torch.Tensor, out: torch.Tensor, ctx, view) -> None:
         """Attention of the step's queries (the first ``n_heads*head_dim`` features of each row of

@@ -8,6 +8,7 @@ off around the call).
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -85,6 +86,9 @@ class Runtime:
         self.large_gemm_rows = 1024
         self.large_gemm_min_fill = 0.8   # least share of the waves of tiles that does work (see takes_large_gemm)
         self.pair_gemm = True       # large products on tcgen05 cta_group::2
+        # q/k-norm, rotation and cache append in the epilogue of the q|k|v product where the pair kernel runs it
+        # (PE_B200_FUSE_QKV_ROPE=0 keeps them kernels of their own, for comparisons)
+        self.fuse_qkv_rope = os.environ.get("PE_B200_FUSE_QKV_ROPE", "1") != "0"
 
     # ---- weights -------------------------------------------------------------------------
     def adopt(self, tensor: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tensor:

@@ -638,6 +638,66 @@ def test_gemm_umma_at_the_layer_shapes_of_an_8b_model(ops, M, N, K, fused, kerne
     assert rel_err(out[pick].double().cpu(), exact) < tol
 
 
+@pytest.mark.parametrize("nh,nkv,K,norm,rotate", [(8, 2, 256, True, True), (3, 1, 320, True, True), (6, 3, 192, False, True),
+                                                  (4, 4, 128, True, False)])
+def test_qkv_product_with_norm_rotation_and_append_in_its_epilogue(ops, nh, nkv, K, norm, rotate):
+    """The q|k|v product with q/k-norm, rotation and cache append in its epilogue against the three kernels it
+    stands for (product, then norm + rotation + append): three sequences, one of which starts in this step and one
+    ends in the middle of a page; 3 and 5 heads' worth of columns do not fill the last 256-column tile.  Queries as
+    the separate kernels leave them, the cache's pages bit for bit except the rounding of the norm's sum."""
+    torch.manual_seed(41)
+    d, dtype = 128, torch.bfloat16
+    lens, q_lens = [300, 130, 200], [230, 130, 136]
+    N = sum(q_lens)
+    x = torch.randn(N, K, device=DEV).to(dtype)
+    w = (torch.randn((nh + 2 * nkv) * d, K, device=DEV) * (1.5 / K ** 0.5)).to(dtype)
+    qw = (1 + 0.2 * torch.randn(d, device=DEV)) if norm else None
+    kw = (1 + 0.2 * torch.randn(d, device=DEV)) if norm else None
+    eps, theta, max_pos = 1e-5, 1e4, 512
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float32), plain.rope_inv_freq(d, theta))
+    cos, sin = (torch.cos(ang).to(DEV), torch.sin(ang).to(DEV)) if rotate else (None, None)
+    token_seq = torch.tensor(sum(([b] * n for b, n in enumerate(q_lens)), []), dtype=torch.int32, device=DEV)
+    pos_list = sum(([lens[b] - q_lens[b] + i for i in range(q_lens[b])] for b in range(3)), [])
+    token_pos = torch.tensor(pos_list, dtype=torch.int32, device=DEV)
+    qstart = torch.tensor([0, q_lens[0], q_lens[0] + q_lens[1], N], dtype=torch.int32, device=DEV)
+    assert ops.gemm_umma2_qkv_rope_supported(x, w, nh, nkv, d, d if rotate else 0)
+    results = []
+    for fused in (False, True):
+        ps = PagedSetup(lens, nkv, d, dtype, seed=41)
+        ld = (nh + 2 * nkv) * d
+        qkv = torch.zeros(N, ld, device=DEV, dtype=dtype)
+        st = _status()
+        if fused:
+            ops.gemm_umma2_qkv_rope(x, w, qkv, nh, nkv, d, qw, kw, eps, cos, sin, d if rotate else 0, token_seq, token_pos,
+                                    ps.seq_slot, qstart, ps.table, ps.num_pages, ps.k_pages, ps.v_pages, True, st)
+        else:
+            ops.gemm_umma2(x, w, qkv, st)
+            ops.qk_norm_rope_append(qkv, N, nh, nkv, d, qw, kw, eps, cos, sin, d if rotate else 0, token_seq, token_pos,
+                                    ps.seq_slot, qstart, ps.table, ps.num_pages, ps.k_pages, ps.v_pages, True, st)
+        assert st.tolist()[0] == 0
+        results.append((qkv[:, : nh * d].float().cpu(), ps.k_pages.float().cpu(), ps.v_pages.float().cpu()))
+    (q0, k0, v0), (q1, k1, v1) = results
+    assert rel_err(q1, q0) < 4e-3 and rel_err(k1, k0) < 4e-3         # one bfloat16 step where the norm's sum rounds differently
+    assert (q1 != q0).float().mean() < 0.02 and (k1 != k0).float().mean() < 0.02
+    assert torch.equal(v1, v0)                                        # values are copied: bit for bit, cleared rows included
+    # and against the plain formulas
+    prod = x.float().cpu() @ w.float().cpu().T
+    prod = prod.to(dtype).float()
+    q_in = prod[:, : nh * d].view(N, nh, d)
+    want = plain.rms_norm(q_in, qw.cpu(), eps) if norm else q_in
+    if rotate:
+        c, s_ = plain.rope_cos_sin(torch.tensor(pos_list), d, theta)
+        want = plain.rope_rotate_neox(want, c, s_, d)
+    assert rel_err(q1.view(N, nh, d), want) < KTOL[dtype]
+    # a layer that only reads a cache: nothing is appended
+    ps = PagedSetup(lens, nkv, d, dtype, seed=41)
+    k_before = ps.k_pages.clone()
+    qkv = torch.zeros(N, (nh + 2 * nkv) * d, device=DEV, dtype=dtype)
+    ops.gemm_umma2_qkv_rope(x, w, qkv, nh, nkv, d, qw, kw, eps, cos, sin, d if rotate else 0, token_seq, token_pos,
+                            ps.seq_slot, qstart, ps.table, ps.num_pages, ps.k_pages, ps.v_pages, False, _status())
+    assert torch.equal(ps.k_pages, k_before) and torch.equal(qkv[:, : nh * d].float().cpu(), q1)
+
+
 def test_sampler_greedy_and_ties(ops):
     torch.manual_seed(8)
     logits = torch.randn(6, 1000, device=DEV)
