@@ -138,8 +138,10 @@ def reference_arm(args):
 
         with open(os.path.join(ROOT, "pytorch-engine_b200", "config", "presets", args.preset + ".json")) as fh:
             cfg = json.load(fh)
-        out = arm.run(cfg, preset_name=args.preset, batch=args.batch, context=args.context, steps=args.steps,
-                      warmup=args.warmup, layers=args.layers)
+        import contextlib
+        with contextlib.redirect_stdout(sys.stderr):     # the reference prints its progress to standard output
+            out = arm.run(cfg, preset_name=args.preset, batch=args.batch, context=args.context, steps=args.steps,
+                          warmup=args.warmup, layers=args.layers)
     except BaseException as exc:  # the arm says why it cannot run; it never fails the benchmark
         if isinstance(exc, KeyboardInterrupt):
             raise
