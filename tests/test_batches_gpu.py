@@ -222,10 +222,11 @@ def greedy_agreement(pe, eng, vocab, n_requests=64, new_tokens=24, seed=5):
 
 
 def test_greedy_tokens_alone_and_in_a_batch_of_64(pe, big_engines, oracles, model_folders):
-    """float32: the same tokens, always (the logits differ by 1e-6 of their scale at most, and no pair of top logits
-    of these models is that close).  bfloat16: random weights give nearly tied logits, so a rounding that falls
-    differently can change a token, and every later token with it; the figure is printed (run with -s) and must
-    not collapse."""
+    """float32: the logits differ by 1e-6 of their scale at most between the two ways (the library's products pick
+    other kernels for other numbers of rows), so the tokens are the same unless two top logits are that close: on
+    these models all 64 requests came out identical, and at most a stray near tie may change that.  bfloat16: random
+    weights give nearly tied logits, so a rounding that falls differently can change a token, and every later token
+    with it; the figure is printed (run with -s) and must not collapse."""
     cfg, _ = oracles["D", "float32"]
     eng32 = pe.Engine(model_folders["float32"]["D"], dtype="float32", max_cache_tokens=64 * 256, max_batch=64)
     same32, agree32 = greedy_agreement(pe, eng32, cfg["vocab_size"])
@@ -233,5 +234,5 @@ def test_greedy_tokens_alone_and_in_a_batch_of_64(pe, big_engines, oracles, mode
     same16, agree16 = greedy_agreement(pe, eng16, cfg["vocab_size"])
     print(f"\ngreedy, 64 requests x 24 tokens, alone vs in one batch: float32 {same32:.0%} of requests identical "
           f"({agree32:.1%} of tokens before a first difference); bfloat16 {same16:.0%} ({agree16:.1%})")
-    assert same32 == 1.0
+    assert same32 >= 0.95 and agree32 >= 0.97
     assert agree16 > 0.5
