@@ -132,3 +132,35 @@ def test_cli_text_prompts_need_a_tokenizer_file(pe, tmp_path, capsys):
     tok.save(str(tmp_path / "m" / "tokenizer.json"))
     loaded = cli.load_tokenizer(str(tmp_path / "m"))
     assert loaded.encode("hello there you").ids == [1, 2, 0]
+
+
+def test_reference_arm_and_plain_baseline_of_the_benchmark_run(pe):
+    """The two things ``bench.py`` compares the engine with, on the CPU at a tiny size: the reference arm (the
+    unmodified reference from ``baseline/_ref``, skipped where that copy is absent; it imports nothing of this
+    package) and the plain PyTorch model."""
+    import importlib.util
+
+    def load(name):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, "baseline", name + ".py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod
+
+    cfg = pe.preset("tiny_b").to_dict()
+    plain_torch = load("plain_torch")
+    m = plain_torch.PlainTorchModel(cfg, cfg["num_hidden_layers"], "cpu", dtype=torch.float32)
+    m.alloc_cache(2, 40)
+    ids = torch.randint(0, cfg["vocab_size"], (2, 20))
+    whole = m.forward(ids, 0, last_only=False)
+    m.alloc_cache(2, 40)
+    head = m.forward(ids[:, :19], 0)
+    last = m.forward(ids[:, 19:], 19)
+    assert whole.shape == (2, 20, cfg["vocab_size"]) and float((last[:, -1] - whole[:, -1]).abs().max()) < 1e-5
+    arm = load("reference_arm")
+    if arm.find_reference() is None:
+        pytest.skip("no copy of the reference under baseline/_ref")
+    pytest.importorskip("gguf")
+    out = arm.run(cfg, preset_name="tiny_b", batch=2, context=64, steps=6, warmup=2, device="cpu", log=lambda m: None)
+    assert out["impl"] == "reference" and "unavailable" not in out
+    assert out["e2e"]["tokens"] == 12 and out["value"] > 0 and out["config"]["layers"] == 3
+    assert "pytorch-engine_b200" not in open(os.path.join(ROOT, "baseline", "reference_arm.py")).read().split('"""', 2)[2]
