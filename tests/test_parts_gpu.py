@@ -867,3 +867,93 @@ def test_state_mixer_under_cuda_graphs_sees_every_token_once(pe):
     finally:
         pe.parts.unregister("mixer", "launch_only_sum")
         pe.config.unregister_architecture("ToyRunningMeanLM")
+
+
+# ---- a block with two mixers: each gets a cache entry of its own ------------------------------------------------
+class TwoMixerBlock:
+    """``out = x + local(norm(x)) + global(norm(x))`` and no feed-forward: two attention mixers (a windowed and a
+    full one) read the same normed input; the block's cache view is a dict by mixer name."""
+
+    graph_safe = True
+
+    def __init__(self, spec, parts, runtime):
+        self.rt, self.p = runtime, parts
+
+    def forward(self, stream, pending, ctx, view, writes_cache=True):
+        normed = ctx.buffer("two.normed", tuple(stream.shape), self.rt.dtype)
+        self.p["norm"].add_forward(stream, pending, normed)
+        # a part's delta lies in a step buffer that the next call of a part of the same class uses again: the two
+        # mixers are both attention, so the first one's output is copied before the second runs
+        a = self.p["local"].forward(normed, ctx, view["local"]).to(torch.float32, copy=True)
+        b = self.p["global"].forward(normed, ctx, view["global"]).float()
+        return (a + b).to(self.rt.dtype)
+
+
+def test_toy_block_with_two_mixers_and_no_feed_forward(pe):
+    P, B, R = pe.parts.PartSpec, pe.parts.BlockSpec, pe.parts.RunStep
+    eps, theta, window = 1e-6, 10000.0, 9
+    cfg = ToyMixConfig(hidden_size=48, vocab_size=101, heads=3, kv_heads=1, head_dim=16, architecture="ToyTwoMixerLM")
+
+    def plan(c):
+        h, d = c.hidden_size, c.head_dim
+        norm = lambda n: P("rmsnorm", {"dim": h, "eps": eps}, {"weight": n})
+        att = lambda tag, win: P("attention", {"hidden": h, "n_heads": c.heads, "n_kv_heads": c.kv_heads, "head_dim": d,
+                                               "qk_norm": False, "eps": eps, "scale": None, "window": win, "position": "rope"},
+                                 {k: f"l0.{tag}.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj")})
+        two = B("two_mixers", {"norm": ("norm", norm("l0.n")), "local": ("mixer", att("local", window)),
+                               "global": ("mixer", att("global", None))}, name="two")
+        usual = B.standard("pre_norm", norm("l1.n1"), att("usual", None), norm("l1.n2"),
+                           P("swiglu", {"hidden": h, "intermediate": 2 * h}, {"gate_proj": "l1.g", "up_proj": "l1.u", "down_proj": "l1.d"}),
+                           name="usual")
+        return pe.parts.ModelPlan(
+            hidden_size=h, vocab_size=c.vocab_size, max_positions=c.max_position_embeddings,
+            embedding=P("token_embedding", {"vocab": c.vocab_size, "hidden": h}, {"weight": "emb"}),
+            blocks=(two, usual), order=(R(0), R(1)), final_norm=norm("fn"),
+            head=P("linear_head", {"vocab": c.vocab_size, "hidden": h}, {"weight": "emb"}),
+            positions={"rope": P("rope", {"rotary_dim": d, "theta": theta, "max_positions": c.max_position_embeddings})})
+
+    pe.parts.register("arrangement", "two_mixers", TwoMixerBlock, replace=True)
+    pe.register_architecture("ToyTwoMixerLM", ToyMixConfig, plan, replace=True)
+    try:
+        eng = pe.Engine.from_random(cfg, seed=31, dtype="float32", max_cache_tokens=256, max_batch=2)
+        # three cache entries in two groups: the windowed mixer's, and the two full ones (block 0's and block 1's)
+        kinds = sorted((g.request.window or 0, [str(e) for e in g.entries]) for g in eng.cache.groups)
+        assert kinds == [(0, ["(0, 'global')", "1"]), (window, ["(0, 'local')"])]
+        w = {k: v.float().cpu() for k, v in pe.weights.random_weights(eng.plan, 31, device=DEV).items()}
+        nH, nKV, d = cfg.heads, cfg.kv_heads, cfg.head_dim
+
+        def attention(n, tag, win):
+            S = n.shape[0]
+            cos, sin = plain.rope_cos_sin(torch.arange(S), d, theta)
+            q = plain.rope_rotate_neox((n @ w[f"{tag}.q_proj"].T).view(S, nH, d), cos, sin, d)
+            k = plain.rope_rotate_neox((n @ w[f"{tag}.k_proj"].T).view(S, nKV, d), cos, sin, d)
+            v = (n @ w[f"{tag}.v_proj"].T).view(S, nKV, d)
+            return plain.causal_gqa_attention(q, k, v, d ** -0.5, window=win).reshape(S, nH * d) @ w[f"{tag}.o_proj"].T
+
+        def plain_toy(tokens):
+            x = w["emb"][tokens]
+            n = plain.rms_norm(x, w["l0.n"], eps)
+            x = x + attention(n, "l0.local", window) + attention(n, "l0.global", None)
+            x = x + attention(plain.rms_norm(x, w["l1.n1"], eps), "l0.usual", None)
+            x = x + plain.swiglu(plain.rms_norm(x, w["l1.n2"], eps), w["l1.g"], w["l1.u"], w["l1.d"])
+            return plain.rms_norm(x, w["fn"], eps) @ w["emb"].T
+
+        seqs = [list(range(5, 45)), [88, 0, 3, 7, 7, 21]]
+        refs = [plain_toy(s) for s in seqs]
+        for rnd in range(2):
+            slots = [eng.alloc_slot(), eng.alloc_slot()]
+            got = [[], []]
+            lg = eng.step([pe.StepEntry(slots[0], seqs[0][:30], (0, 29)), pe.StepEntry(slots[1], seqs[1][:2], (1,))])
+            got[0] += [lg[0].cpu(), lg[1].cpu()]; got[1].append(lg[2].cpu())
+            for k in range(4):
+                lg = eng.step([pe.StepEntry(slots[0], [seqs[0][30 + k]], (0,)), pe.StepEntry(slots[1], [seqs[1][2 + k]], (0,))])
+                got[0].append(lg[0].cpu()); got[1].append(lg[1].cpu())
+            for s in slots:
+                eng.free_slot(s)
+            e0 = [rel_err(g, r) for g, r in zip(got[0], refs[0][[0, 29, 30, 31, 32, 33]])]
+            e1 = [rel_err(g, r) for g, r in zip(got[1], refs[1][[1, 2, 3, 4, 5]])]
+            assert max(e0) < 1e-5 and max(e1) < 1e-5, (rnd, e0, e1)
+        eng.cache.check()
+    finally:
+        pe.parts.unregister("arrangement", "two_mixers")
+        pe.config.unregister_architecture("ToyTwoMixerLM")
