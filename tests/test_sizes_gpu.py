@@ -16,6 +16,9 @@ pytestmark = pytest.mark.gpu
     # K = 4,096 and 12,288, attention on the tcgen05 prefill kernel (one layer and a small vocabulary keep the
     # plain implementation on the CPU to some seconds)
     ("qwen3_8b", 1, (1200, 41), {"vocab_size": 8192}),
+    # and of more than 2,048, where the output and down projections fill enough 256 x 256 tiles to run on the pair
+    # kernel as well (at 1,200 rows they go to the library); two layers
+    ("qwen3_8b", 2, (2100, 41), {"vocab_size": 4096}),
 ])
 def test_parity_at_a_qwen3_size(preset, layers, lengths, extra):
     worst = run(preset, layers, lengths=lengths, verbose=False, **extra)
