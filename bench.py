@@ -207,7 +207,8 @@ def main():
     B, ctx, K, W = args.batch, args.context, args.steps, args.warmup
     max_b = max(B, 64 if not args.no_points else B)
     t_load = time.perf_counter()
-    engine = pe.Engine.from_random(cfg, seed=0, dtype="bfloat16", max_context_len=ctx, max_cache_tokens=max_b * ctx,
+    # the cache holds whole pages of 64 tokens: a context that is no multiple of 64 still takes its last page
+    engine = pe.Engine.from_random(cfg, seed=0, dtype="bfloat16", max_context_len=ctx, max_cache_tokens=max_b * (-(-ctx // 64) * 64),
                                    max_batch=max_b, enable_cuda_graph=not args.no_cuda_graph)
     for g in engine.cache.groups:
         if g.storage is not None:
