@@ -351,6 +351,8 @@ def check_drawn_tokens(cfg: dict, w: Dict[str, torch.Tensor], prompt: Sequence[i
     differed = 0
     for j, tok in enumerate(tokens):
         row = forward_logits(cfg, w, toks)[-1]
+        if filters.get("repetition_penalty", 1.0) != 1.0:
+            filters["recent_tokens"] = list(toks)    # the penalty looks at the prompt and what has been drawn so far
         scores = gumbel_scores(row, seed=seed, request=request, step=j, **filters)
         if scores is None:
             scores = filter_logits(row, **filters)[0].to(torch.float64)

@@ -373,6 +373,28 @@ def test_seeded_sampling_does_not_depend_on_batching(pe, engines, oracles):
     assert differed <= 2          # near ties may fall the other way; they are rare
 
 
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_repetition_penalty_through_generation(pe, engines, oracles, temperature):
+    """A repetition penalty of 1.6, greedy and sampled, for three prompts of unequal lengths in one batch: every
+    token is the plain implementation's draw from its own logits with the penalty on the prompt and on what has
+    been drawn so far; the penalised greedy run differs from the run without."""
+    cfg, w = oracles["A"]
+    prompts = [_tokens(cfg["vocab_size"], n, 90 + n) for n in (5, 23, 2)]
+    kw = dict(max_tokens=12, temperature=temperature, top_k=0, top_p=1.0, min_p=0.0, seed=5)
+    eng = engines("A", "float32")
+    pen = eng.generate(prompts, pe.SamplingParams(repetition_penalty=1.6, **kw))
+    differed = 0
+    for r, res in enumerate(pen):
+        assert res.completion_tokens == 12
+        differed += plain.check_drawn_tokens(cfg, w, prompts[r], res.token_ids, seed=5, request=r, margin=1e-3,
+                                             temperature=temperature, repetition_penalty=1.6)
+    assert differed <= 1
+    if temperature == 0.0:
+        # (a sampled draw with the same random numbers and slightly shifted probabilities often stays the same)
+        free = eng.generate(prompts, pe.SamplingParams(**kw))
+        assert [r.token_ids for r in pen] != [r.token_ids for r in free]
+
+
 def test_cache_too_small_is_an_error_not_a_wrong_result(pe, engines, oracles):
     cfg, w = oracles["A"]
     eng = engines("A", "float32", max_cache_tokens=128, max_context_len=128)
