@@ -121,24 +121,6 @@ __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(tma::smem_addr(bar)) : "memory");
 }
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// the same with the A operand read from tensor memory (row = lane, two bfloat16 per 32-bit column, so a
-// K = 16 step takes 8 columns)
-__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
@@ -162,22 +144,72 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
-// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) {
-  return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
-         ((uint64_t)2 << 61);
-}
-// MN-major operand, 128-byte swizzle: 64 elements of the N dimension are contiguous (128 bytes); the
-// next 64 lie `lbo` bytes further; along K, rows are 128 bytes apart in groups of 8 (1024 bytes).
-__device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr, uint32_t lbo_bytes) {
-  return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) | ((uint64_t)(1024 >> 4) << 32) |
-         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
 // kind::f16 instruction descriptor: float32 D, bfloat16 A and B, A K-major; b_mn: B is MN-major (bit 16).
 __host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// The MMA-issuing thread is one thread that issues one instruction after the other, and its loop sets a block's
+// pace: a product's k-step or a commit costs it some 70 cycles, a wait well over a hundred even on a barrier that is
+// long complete.  Whatever it does between those counts as well: the 64-bit operand descriptors' constant upper
+// word (1,024 bytes between 8-row groups, descriptor version, 128-byte swizzle) is set once, the lower word
+// (start address in 16-byte units; for an MN-major operand also the distance between its two 64-column halves)
+// is advanced by adding constants, and the k-steps of a product are issued from one block of instructions.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1,024 bytes apart.
+__device__ __forceinline__ uint32_t desc_lo_k_major(uint32_t saddr) { return ((saddr >> 4) & 0x3FFF) | (1u << 16); }
+// MN-major operand, 128-byte swizzle: 64 elements of the N dimension are contiguous (128 bytes); the next 64 lie
+// `lbo` bytes further; along K, rows are 128 bytes apart in groups of 8 (1,024 bytes).
+__device__ __forceinline__ uint32_t desc_lo_mn_major(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr >> 4) & 0x3FFF) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+
+// S = Q.K^T of one page: eight k-steps of 16 features.  Both operands are two 64-feature halves of [rows][128 B]:
+// a k-step moves 32 bytes (2 units) inside a half, the second half lies rows * 128 bytes further (A: 128 rows,
+// 1,024 units; B: 64 keys, 512 units).
+#define PE_QK_STEP(A, B)                                                                       \
+  "add.u32 al, %1, " #A ";\n"                                                                  \
+  "add.u32 bl, %2, " #B ";\n"                                                                  \
+  "mov.b64 da, {al, %3};\n"                                                                    \
+  "mov.b64 db, {bl, %3};\n"                                                                    \
+  "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pt;\n"
+__device__ __forceinline__ void umma_qk_page(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+  asm volatile(
+      "{\n"
+      ".reg .pred pf, pt;\n"
+      ".reg .b64 da, db;\n"
+      ".reg .b32 al, bl;\n"
+      "setp.ne.b32 pf, %4, %4;\n"
+      "setp.eq.b32 pt, %4, %4;\n"
+      "mov.b64 da, {%1, %3};\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, pf;\n"
+      PE_QK_STEP(2, 2) PE_QK_STEP(4, 4) PE_QK_STEP(6, 6)
+      PE_QK_STEP(1024, 512) PE_QK_STEP(1026, 514) PE_QK_STEP(1028, 516) PE_QK_STEP(1030, 518)
+      "}\n" ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(idesc) : "memory");
+}
+#undef PE_QK_STEP
+// O (+)= P.V of one page: four k-steps of 16 keys.  P comes from tensor memory (8 columns of bfloat16 pairs a
+// step), V is MN-major: 16 keys are 16 rows of 128 bytes (128 units).  `accumulate` == 0: the first step starts O.
+#define PE_PV_STEP(T, B)                                                                       \
+  "add.u32 ta, %1, " #T ";\n"                                                                  \
+  "add.u32 bl, %2, " #B ";\n"                                                                  \
+  "mov.b64 db, {bl, %3};\n"                                                                    \
+  "tcgen05.mma.cta_group::1.kind::f16 [%0], [ta], db, %4, pt;\n"
+__device__ __forceinline__ void umma_pv_page(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p0, pt;\n"
+      ".reg .b64 db;\n"
+      ".reg .b32 ta, bl;\n"
+      "setp.ne.b32 p0, %5, 0;\n"
+      "setp.eq.b32 pt, %4, %4;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p0;\n"
+      PE_PV_STEP(8, 128) PE_PV_STEP(16, 256) PE_PV_STEP(24, 384)
+      "}\n" ::"r"(d_tmem), "r"(p_tmem), "r"(v_lo), "r"(kDescHi), "r"(idesc), "r"(accumulate) : "memory");
+}
+#undef PE_PV_STEP
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -230,16 +262,19 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
   char* v_s = k_s + kKStages * kPageBytes;   // kVStages V pages
   uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + kVStages * kPageBytes);
   uint64_t& q_full = bars[0];
+  // The MMA thread's commits are few on purpose: that thread issues one instruction after the other, a commit costs
+  // it about as much as a product's k-step, and its loop sets a block's pace.  So a barrier serves every purpose it
+  // can: S of a page being there also says that the page's K stage is spent (a K stage and an S buffer have the
+  // same index), and a V stage being spent also says that the page's P.V product is done.
   uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* k_empty = bars + 3;   // [2]
   uint64_t* v_full = bars + 5;    // [3]
-  uint64_t* v_empty = bars + 8;   // [3]
-  uint64_t* s_full = bars + 11;   // [2]
+  uint64_t* v_empty = bars + 8;   // [3]: the page's P.V product is done: the stage may be filled again, O may be
+                                  //      rescaled, the S after next may overwrite the page's P
+  uint64_t* s_full = bars + 11;   // [2]: S of a page is in the buffer, and the page's K stage may be filled again
   uint64_t* p_ready = bars + 13;  // [2]: one per S buffer, the softmax may be a page ahead of the P.V products
-  uint64_t& pv_done = bars[15];   // one phase per page: waited for only before O is rescaled
   uint64_t& o_done = bars[16];    // one phase per item: its last P.V product is done.  (A barrier of its own: the
-                                  // softmax does not follow pv_done phase by phase, and a parity wait that is two
-                                  // phases ahead of the barrier passes at once.)
+                                  // softmax does not follow the pages' products phase by phase, and a parity wait
+                                  // that is two phases ahead of its barrier passes at once.)
   uint64_t& q_empty = bars[17];   // one phase per item: its last S product has read Q
   uint64_t& o_free = bars[18];    // one phase per item: the softmax threads have read O out
   uint64_t* w_full = bars + 19;   // [2]: a rank has been put into the slot
@@ -264,7 +299,6 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
     tma::mbar_init(&q_full, 1);
     for (int s = 0; s < 2; ++s) {
       tma::mbar_init(&k_full[s], 1);
-      tma::mbar_init(&k_empty[s], 1);
       tma::mbar_init(&s_full[s], 1);
       tma::mbar_init(&p_ready[s], 128);
     }
@@ -272,7 +306,6 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
       tma::mbar_init(&v_full[s], 1);
       tma::mbar_init(&v_empty[s], 1);
     }
-    tma::mbar_init(&pv_done, 1);
     tma::mbar_init(&o_done, 1);
     tma::mbar_init(&q_empty, 1);
     tma::mbar_init(&o_free, 128);
@@ -347,7 +380,7 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
           }
           const int y = (page * a.n_kv_heads + w.kvh) * BN;
           const int ks = g % kKStages, vs = g % kVStages;
-          if (!tma::mbar_wait(&k_empty[ks], ((g / kKStages) & 1) ^ 1)) {
+          if (!tma::mbar_wait(&s_full[ks], ((g / kKStages) & 1) ^ 1)) {   // K stage and S buffer of a page have the same index
             report(a.status, kStatusWaitTimedOut, 20, me, j);
             failed = 1;
             break;
@@ -375,7 +408,9 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
     if (lane == 0) {
       const uint32_t idesc_qk = instr_desc(BM, BN, false);
       const uint32_t idesc_pv = instr_desc(BM, HD, true);
-      const uint32_t q_addr = tma::smem_addr(q_s);
+      const uint32_t q_lo = desc_lo_k_major(tma::smem_addr(q_s));
+      const uint32_t k_lo0 = desc_lo_k_major(tma::smem_addr(k_s));               // stage s: + s * (16 KB / 16)
+      const uint32_t v_lo0 = desc_lo_mn_major(tma::smem_addr(v_s), BN * 128);
       bool ok = true;
       for (uint32_t f = 0; ok && !failed; ++f) {
         if (!tma::mbar_wait(&w_full[f & 1], (f >> 1) & 1)) { ok = false; break; }
@@ -390,15 +425,8 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
           const int st = g & 1, ks = g % kKStages;
           if (!tma::mbar_wait(&k_full[ks], (g / kKStages) & 1)) return false;
           fence_after_sync();
-          const uint32_t k_addr = tma::smem_addr(k_s + ks * kPageBytes);
-#pragma unroll
-          for (int k = 0; k < HD / 16; ++k) {
-            const uint32_t off_a = (k >> 2) * (BM * 128) + (k & 3) * 32;
-            const uint32_t off_b = (k >> 2) * (BN * 128) + (k & 3) * 32;
-            umma_bf16(tmem_base + st * BN, desc_k_major(q_addr + off_a), desc_k_major(k_addr + off_b), idesc_qk, k > 0 ? 1u : 0u);
-          }
+          umma_qk_page(tmem_base + st * BN, q_lo, k_lo0 + ((uint32_t)ks << 10), idesc_qk);
           umma_commit(&s_full[st]);     // S is there ...
-          umma_commit(&k_empty[ks]);    // ... and the K page is spent
           if (j == n_tiles - 1) umma_commit(&q_empty);   // ... and so is Q, after the item's last S product
           return true;
         };
@@ -410,7 +438,7 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
           // of one thread run in issue order on today's hardware; the wait makes the order explicit and
           // costs nothing, the softmax of page j is still running.)  Across items nothing is pending: an
           // item ends with all its products complete.
-          if (j >= 1 && j + 1 < n_tiles && !tma::mbar_wait(&pv_done, (g - 1) & 1)) { ok = false; break; }
+          if (j >= 1 && j + 1 < n_tiles && !tma::mbar_wait(&v_empty[(g - 1) % kVStages], ((g - 1) / kVStages) & 1)) { ok = false; break; }
           if (j + 1 < n_tiles) ok = issue_qk(j + 1);        // S of the next page while this one's softmax runs
           if (!ok) break;
           const int st = g & 1, vs = g % kVStages;
@@ -419,14 +447,9 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
           // the first product of an item starts O anew: the item before must have been read out of it
           if (j == 0 && !tma::mbar_wait(&o_free, (it & 1) ^ 1)) { ok = false; break; }
           fence_after_sync();
-          const uint32_t p_tmem = tmem_base + st * BN;       // P lies where S of this page was (bfloat16 pairs, 32 columns)
-          const uint32_t v_addr = tma::smem_addr(v_s + vs * kPageBytes);
-#pragma unroll
-          for (int k = 0; k < BN / 16; ++k)
-            umma_bf16_a_tmem(tmem_o, p_tmem + k * 8, desc_mn_major(v_addr + k * 16 * 128, BN * 128), idesc_pv,
-                             (j > 0 || k > 0) ? 1u : 0u);
-          umma_commit(&v_empty[vs]);
-          umma_commit(&pv_done);
+          // P lies where S of this page was (bfloat16 pairs, 32 columns)
+          umma_pv_page(tmem_o, tmem_base + st * BN, v_lo0 + ((uint32_t)vs << 10), idesc_pv, j > 0 ? 1u : 0u);
+          umma_commit(&v_empty[vs]);    // the V page is spent, and whoever waits for this product may go on
         }
         if (ok) {
           umma_commit(&o_done);
@@ -503,7 +526,7 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
         const bool grow = mx > m_ref + kRescaleThreshold;
         if (__any_sync(0xffffffffu, grow && j > 0 && m_ref != -INFINITY)) {
           // O is rescaled in place: the previous P.V must be done with it first
-          if (!tma::mbar_wait(&pv_done, (g - 1) & 1)) { ok = false; break; }
+          if (!tma::mbar_wait(&v_empty[(g - 1) % kVStages], ((g - 1) / kVStages) & 1)) { ok = false; break; }
           fence_after_sync();
           const float f = (grow && m_ref != -INFINITY) ? fast_exp2(m_ref - mx) : 1.0f;
 #pragma unroll 1
