@@ -266,8 +266,9 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
   // it about as much as a product's k-step, and its loop sets a block's pace.  So a barrier serves every purpose it
   // can: S of a page being there also says that the page's K stage is spent (a K stage and an S buffer have the
   // same index), and a V stage being spent also says that the page's P.V product is done.
-  uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* v_full = bars + 5;    // [3]
+  uint64_t& k0_full = bars[1];    // one phase per item: K of its first page is there
+  uint64_t* kv_full = bars + 5;   // [3], by V stage: V of a page and K of the page after it (copied together, so that
+                                  //      the MMA thread waits once a page for both) are there
   uint64_t* v_empty = bars + 8;   // [3]: the page's P.V product is done: the stage may be filled again, O may be
                                   //      rescaled, the S after next may overwrite the page's P
   uint64_t* s_full = bars + 11;   // [2]: S of a page is in the buffer, and the page's K stage may be filled again
@@ -297,13 +298,13 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
 
   if (tid == 0) {
     tma::mbar_init(&q_full, 1);
+    tma::mbar_init(&k0_full, 1);
     for (int s = 0; s < 2; ++s) {
-      tma::mbar_init(&k_full[s], 1);
       tma::mbar_init(&s_full[s], 1);
       tma::mbar_init(&p_ready[s], 128);
     }
     for (int s = 0; s < kVStages; ++s) {
-      tma::mbar_init(&v_full[s], 1);
+      tma::mbar_init(&kv_full[s], 1);
       tma::mbar_init(&v_empty[s], 1);
     }
     tma::mbar_init(&o_done, 1);
@@ -368,8 +369,8 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
         tma::mbar_expect_tx(&q_full, (uint32_t)(rows_blk * HD * 2));
         load_3d(q_s, &qmap, 0, w.kvh * group, w.q0 + w.tok0, &q_full);
         load_3d(q_s + kQBytes / 2, &qmap, 64, w.kvh * group, w.q0 + w.tok0, &q_full);
-        for (int j = 0; j < w.n_tiles && !failed; ++j) {
-          const uint32_t g = n + j;
+        // Row of the page table's page for the item's page j in the K and V tensors' 2-D views.
+        auto page_row = [&](int j) -> int {
           const int k0 = w.k_begin + j * BN;
           const int logical = k0 / BN;
           int page = -1;
@@ -378,26 +379,43 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
             report(a.status, kStatusPageOutOfRange, w.slot, page, k0);
             page = 0;
           }
-          const int y = (page * a.n_kv_heads + w.kvh) * BN;
-          const int ks = g % kKStages, vs = g % kVStages;
-          if (!tma::mbar_wait(&s_full[ks], ((g / kKStages) & 1) ^ 1)) {   // K stage and S buffer of a page have the same index
-            report(a.status, kStatusWaitTimedOut, 20, me, j);
-            failed = 1;
-            break;
-          }
-          char* kd = k_s + ks * kPageBytes;
-          tma::mbar_expect_tx(&k_full[ks], kPageBytes);
-          tma::load_2d(kd, &kmap, 0, y, &k_full[ks]);
-          tma::load_2d(kd + BN * 128, &kmap, 64, y, &k_full[ks]);
-          if (!tma::mbar_wait(&v_empty[vs], ((g / kVStages) & 1) ^ 1)) {
+          return (page * a.n_kv_heads + w.kvh) * BN;
+        };
+        // K of page g goes into K stage g mod 2, which is free once S of page g - 2 is there (the S buffer of that
+        // index has the stage's number)
+        auto k_stage_free = [&](uint32_t g) -> bool {
+          return tma::mbar_wait(&s_full[g % kKStages], ((g / kKStages) & 1) ^ 1);
+        };
+        auto load_k = [&](uint32_t g, int y, uint64_t* bar) {
+          char* kd = k_s + (g % kKStages) * kPageBytes;
+          tma::load_2d(kd, &kmap, 0, y, bar);
+          tma::load_2d(kd + BN * 128, &kmap, 64, y, bar);
+        };
+        int y = page_row(0);
+        // the first page's K alone; every later K page travels with the V page before it
+        if (!k_stage_free(n)) {
+          report(a.status, kStatusWaitTimedOut, 20, me, 0);
+          failed = 1;
+          continue;
+        }
+        tma::mbar_expect_tx(&k0_full, kPageBytes);
+        load_k(n, y, &k0_full);
+        for (int j = 0; j < w.n_tiles && !failed; ++j) {
+          const uint32_t g = n + j;
+          const int vs = g % kVStages;
+          const bool more = j + 1 < w.n_tiles;
+          const int y_next = more ? page_row(j + 1) : 0;
+          if (!tma::mbar_wait(&v_empty[vs], ((g / kVStages) & 1) ^ 1) || (more && !k_stage_free(g + 1))) {
             report(a.status, kStatusWaitTimedOut, 24, me, j);
             failed = 1;
             break;
           }
           char* vd = v_s + vs * kPageBytes;
-          tma::mbar_expect_tx(&v_full[vs], kPageBytes);
-          tma::load_2d(vd, &vmap, 0, y, &v_full[vs]);
-          tma::load_2d(vd + BN * 128, &vmap, 64, y, &v_full[vs]);
+          tma::mbar_expect_tx(&kv_full[vs], more ? 2 * kPageBytes : kPageBytes);
+          tma::load_2d(vd, &vmap, 0, y, &kv_full[vs]);
+          tma::load_2d(vd + BN * 128, &vmap, 64, y, &kv_full[vs]);
+          if (more) load_k(g + 1, y_next, &kv_full[vs]);
+          y = y_next;
         }
         n += w.n_tiles;
         ++it;
@@ -420,18 +438,17 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
         Item w;
         if (rank >= total || !item_at(a, rank, rows_blk, w)) continue;
         const int n_tiles = w.n_tiles;
-        auto issue_qk = [&](int j) -> bool {
+        // S of the item's page j; its K page is there (the caller has waited for the barrier that counts it)
+        auto issue_qk = [&](int j) {
           const uint32_t g = n + j;
           const int st = g & 1, ks = g % kKStages;
-          if (!tma::mbar_wait(&k_full[ks], (g / kKStages) & 1)) return false;
           fence_after_sync();
           umma_qk_page(tmem_base + st * BN, q_lo, k_lo0 + ((uint32_t)ks << 10), idesc_qk);
-          umma_commit(&s_full[st]);     // S is there ...
+          umma_commit(&s_full[st]);     // S is there, and the K stage is spent
           if (j == n_tiles - 1) umma_commit(&q_empty);   // ... and so is Q, after the item's last S product
-          return true;
         };
-        ok = tma::mbar_wait(&q_full, it & 1);
-        if (ok) ok = issue_qk(0);
+        ok = tma::mbar_wait(&q_full, it & 1) && tma::mbar_wait(&k0_full, it & 1);
+        if (ok) issue_qk(0);
         for (int j = 0; ok && j < n_tiles; ++j) {
           const uint32_t g = n + j;
           // S of page j + 1 goes where P of page j - 1 lies: that P.V product must have read it.  (Products
@@ -439,11 +456,11 @@ prefill_umma_kernel(Args a, const __grid_constant__ CUtensorMap qmap, const __gr
           // costs nothing, the softmax of page j is still running.)  Across items nothing is pending: an
           // item ends with all its products complete.
           if (j >= 1 && j + 1 < n_tiles && !tma::mbar_wait(&v_empty[(g - 1) % kVStages], ((g - 1) / kVStages) & 1)) { ok = false; break; }
-          if (j + 1 < n_tiles) ok = issue_qk(j + 1);        // S of the next page while this one's softmax runs
-          if (!ok) break;
           const int st = g & 1, vs = g % kVStages;
+          // V of this page and K of the next arrive together
+          if (!tma::mbar_wait(&kv_full[vs], (g / kVStages) & 1)) { ok = false; break; }
+          if (j + 1 < n_tiles) issue_qk(j + 1);             // S of the next page while this one's softmax runs
           if (!tma::mbar_wait(&p_ready[st], (g >> 1) & 1)) { ok = false; break; }
-          if (!tma::mbar_wait(&v_full[vs], (g / kVStages) & 1)) { ok = false; break; }
           // the first product of an item starts O anew: the item before must have been read out of it
           if (j == 0 && !tma::mbar_wait(&o_free, (it & 1) ^ 1)) { ok = false; break; }
           fence_after_sync();
