@@ -8,12 +8,14 @@
 // zero and is never stored).  It walks the sequence's 64-key pages.  Roles:
 //   warp 5    TMA producer: Q once (a 3-D box [tokens][group heads][64 features] per feature half),
 //             then K pages into a ring of two (a K page is spent as soon as S is there) and V pages
-//             into a ring of three (needed until P.V), each ring with barriers of its own, so that a
-//             page's copy starts two pages ahead;
+//             into a ring of three (needed until P.V), so that a page's copy starts two pages ahead.  The
+//             first page's K has a barrier of its own; after it, a page's V and the next page's K are
+//             copied onto one barrier;
 //   warp 4    MMA issuer: S = Q.K^T (128 x 64, eight k-steps of 16) into one of two S accumulators in
 //             tensor memory, and O += P.V (128 x 128, four k-steps of 16 keys) with P as the A operand
 //             from tensor memory and V as an MN-major operand from shared memory, so the page that TMA
-//             wrote as [keys][features] needs no transpose;
+//             wrote as [keys][features] needs no transpose.  Its loop is what a block's pace hangs on, and
+//             it is one thread: per page it waits three times and commits twice (see the barriers' list);
 //   warps 0-3 softmax: thread r owns row r.  It reads its S row from TMEM (tcgen05.ld), scales and
 //             masks (pages below the diagonal need no mask), keeps the running maximum and sum in
 //             registers, writes P as bfloat16 pairs back over the S columns it has read (tcgen05.st: P
