@@ -90,6 +90,10 @@ int pe_repetition_penalty(float* logits, long long ld, int n_rows, int vocab, co
 // swiglu.cu
 int pe_silu_mul(int dtype, const void* gate_up, void* out, int n_rows, int inter, cudaStream_t stream);
 
+// wait_probe.cu
+int pe_wait_probe(unsigned long long* out, int polls, cudaStream_t stream);
+long long pe_wait_limit_polls();
+
 #ifdef __cplusplus
 }
 #endif

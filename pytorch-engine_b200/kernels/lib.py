@@ -60,9 +60,11 @@ _SIGNATURES = {
     "pe_attention_mma_decode_blocks_per_sm": [I],
     "pe_attention_umma_prefill": [P, L, L, P, L, I, I, I, I, I, F, I, P, P, P, P, I, I, P, P, I, P, P, P],
     "pe_attention_umma_supported": [I, I, I],
+    "pe_wait_probe": [P, I, P],
     "pe_attention_decode_noalloc": [I, P, L, P, L, I, I, I, I, F, I, P, P, P, P, I, I, P, P, I, I, P, P],
 }
-_RESTYPES = {"pe_attention_generic_scratch_floats": (L, [I, I, I, I]),
+_RESTYPES = {"pe_wait_limit_polls": (L, []),
+             "pe_attention_generic_scratch_floats": (L, [I, I, I, I]),
              "pe_sample_scratch_bytes": (L, [I, I, F, I, F, F])}
 
 

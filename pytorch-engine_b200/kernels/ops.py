@@ -368,3 +368,19 @@ def repetition_penalty(logits: torch.Tensor, recent: torch.Tensor, recent_count:
     check(library().pe_repetition_penalty(_ptr(logits), logits.stride(0), n, vocab, _ptr(recent), recent.shape[1],
                                           _ptr(recent_count), float(penalty), _stream()), "repetition_penalty")
     _count(1)
+
+
+def wait_poll_seconds(device, polls: int = 20000) -> float:
+    """Seconds that one poll of an mbarrier takes when the phase it asks for is not complete (csrc/wait_probe.cu):
+    ``polls`` polls of a barrier on which nothing arrives, timed on the device."""
+    out = torch.zeros(2, dtype=torch.int64, device=device)
+    check(library().pe_wait_probe(_ptr(out), int(polls), _stream()), "wait_probe")
+    _count(1)
+    ns, passed = out.tolist()
+    _need(passed == 0, "wait_probe: a poll of a barrier that nothing arrives on passed")
+    return ns * 1e-9 / polls
+
+
+def wait_limit_seconds(device) -> float:
+    """The longest that a bounded wait inside a kernel of this library lasts before it gives up."""
+    return int(library().pe_wait_limit_polls()) * wait_poll_seconds(device)

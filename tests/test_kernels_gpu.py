@@ -832,3 +832,13 @@ def test_unsupported_sizes_are_refused(pe, ops):
                               torch.zeros(1, 1, dtype=torch.int32, device=DEV), 1, q, q, None, 0, 0, _status())
     with pytest.raises(pe.kernels.KernelError):
         ops.embed_gather(torch.zeros(4, 4), torch.zeros(1, dtype=torch.int32), torch.zeros(1, 4), torch.zeros(4, dtype=torch.int32))
+
+
+def test_a_bounded_wait_gives_up_within_seconds(ops):
+    """Every wait inside a kernel polls an mbarrier a limited number of times.  A poll that finds the phase incomplete
+    takes microseconds (the hardware parks the thread for a while), so the limit in polls is a limit in time: the
+    probe kernel polls a barrier on which nothing arrives, a counted number of times, and ends by itself."""
+    poll = ops.wait_poll_seconds(DEV, polls=20000)
+    assert 1e-7 < poll < 2e-5, f"one failing poll took {poll * 1e6:.2f} us"
+    limit = ops.wait_limit_seconds(DEV)
+    assert 0.5 < limit < 10.0, f"a wait that nothing ends would last {limit:.1f} s"
